@@ -2,13 +2,16 @@
 architecture's own config.json reader."""
 from .specs import (AttentionSpec, DenseMLPSpec, GatedLinearAttentionSpec, GatedMLPSpec, LayerSpec, LinearAttentionSpec,
                     MaskedAttentionSpec, ModelSpec, OnePlusRMSNormSpec, ParallelMixerSpec, PostNormLayerSpec, RMSNormSpec,
-                    RotaryHalfSpec, RotaryPartSpec, RoutedMLPSpec, ScalarRMSNormSpec, ScheduleEntry, SinusoidSpec)
+                    RotaryHalfSpec, RotaryPairsSpec, RotaryPartSpec, RoutedMLPSpec, SandwichLayerSpec, ScalarRMSNormSpec, ScheduleEntry,
+                    SinusoidSpec, UnitRMSNormSpec, LatentAttentionSpec)
 from .base import ConfigError, ModelConfig
 from .nilivik import NilivikConfig
 from .pibulix import PibulixConfig
 from .qwen3 import Qwen3Config
+from .venidra import VenidraConfig
 
 __all__ = ["AttentionSpec", "DenseMLPSpec", "GatedMLPSpec", "LayerSpec", "LinearAttentionSpec", "MaskedAttentionSpec",
            "ModelSpec", "ParallelMixerSpec", "RMSNormSpec", "RotaryHalfSpec", "ScalarRMSNormSpec", "ScheduleEntry",
            "SinusoidSpec", "ConfigError", "ModelConfig", "NilivikConfig", "Qwen3Config", "PibulixConfig",
-           "GatedLinearAttentionSpec", "OnePlusRMSNormSpec", "PostNormLayerSpec", "RotaryPartSpec", "RoutedMLPSpec"]
+           "GatedLinearAttentionSpec", "OnePlusRMSNormSpec", "PostNormLayerSpec", "RotaryPartSpec", "RoutedMLPSpec", "VenidraConfig", "LatentAttentionSpec", "RotaryPairsSpec",
+           "SandwichLayerSpec", "UnitRMSNormSpec"]

@@ -12,9 +12,11 @@ from typing import Any, Optional, Tuple
 
 @dataclass(frozen=True)
 class RMSNormSpec:
-    """y = w * x * rsqrt(mean(x^2) + eps) over the last ``dim`` elements."""
+    """y = w * x * rsqrt(mean(x^2) + eps) over the last ``dim`` elements. ``tensor``: the weight's name under the
+    part's prefix (empty: the prefix itself names it)."""
     dim: int
     eps: float
+    tensor: str = "weight"
 
 
 @dataclass(frozen=True)
@@ -27,6 +29,13 @@ class ScalarRMSNormSpec:
 @dataclass(frozen=True)
 class OnePlusRMSNormSpec:
     """y = (1 + w) * x * rsqrt(mean(x^2) + eps): an RMS norm whose stored weight sits around zero."""
+    dim: int
+    eps: float
+
+
+@dataclass(frozen=True)
+class UnitRMSNormSpec:
+    """y = x * rsqrt(mean(x^2) + eps) over the last ``dim`` elements: an RMS norm without a weight."""
     dim: int
     eps: float
 
@@ -51,6 +60,14 @@ class RotaryPartSpec:
     """Rotate-half rotation of the first ``dim`` coordinates of a head (coordinate i with i + dim/2, i below
     dim/2) by angle(p, i) = p * base^(-2i/dim); the head's other coordinates pass. The frequencies are made in
     float64 and rounded to float32 once; the angle is their float32 product with the position."""
+    dim: int
+    base: float
+
+
+@dataclass(frozen=True)
+class RotaryPairsSpec:
+    """Rotation of neighbouring pairs over the first ``dim`` coordinates of a vector (coordinate 2i with 2i + 1, i below
+    dim/2) by angle(p, i) = p * base^(-2i/dim); the other coordinates pass. Frequencies and angles as ``RotaryPartSpec``."""
     dim: int
     base: float
 
@@ -82,7 +99,11 @@ class MaskedAttentionSpec:
     denominator is one plus the sum; no tensor); and what may stand between the projection and the cache:
     ``conv_taps`` (a causal convolution over time of that many taps on every channel of q, k and v, tensors
     ``<q|k|v>.conv`` [channels, taps], its memory a per-sequence state), ``qk_norm`` (a norm spec over
-    head_dim for q and k heads, tensors ``q.norm`` / ``k.norm``) and ``position`` (a ``RotaryPartSpec``)."""
+    head_dim for q and k heads, tensors ``q.norm`` / ``k.norm``; a ``UnitRMSNormSpec`` has no tensors) and ``position``
+    (a ``RotaryPartSpec``); the norm comes before the rotation unless ``norm_after_rotation``.
+    ``value_mix``: the layers of a model that say it share the values of the first of them ("source": it leaves its
+    values of the step's tokens for the others and caches them as they are); every other ("blend") caches and uses
+    v <- (1 - lam) v + lam v_source with its learned number ``vmix`` (both kinds hold the tensor; the source's is unused)."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -100,6 +121,30 @@ class MaskedAttentionSpec:
     conv_taps: Optional[int] = None
     qk_norm: Optional[Any] = None
     position: Optional[Any] = None
+    norm_after_rotation: bool = False
+    value_mix: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose queries, keys and values come through low-rank latents. With x the mixer's input:
+    c_q = norm(W_dq x) (weight ``dq.norm``), q = W_uq c_q laid out head by head as [head_dim plain | rot_dim rotated];
+    W_dkv x has kv_rank + rot_dim rows: the first kv_rank, normed (weight ``dkv.norm``), are the latent c, the last
+    rot_dim, rotated by ``position`` and not normed, are one key part all heads share. Per head the plain key is
+    W_uk c and the value W_uv c; score = (q_plain . k_plain + q_rot . k_rot) * scale; causal, inside ``window`` and/or
+    ``chunk``; softmax; output projection ``o`` on the concatenated heads. The cache holds c and the rotated key part only."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    position: Optional[Any] = None
+    window: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -210,6 +255,22 @@ class PostNormLayerSpec:
 
 
 @dataclass(frozen=True)
+class SandwichLayerSpec:
+    """One block with a norm before and after each sublayer: x <- x + norm_mix_out(mixer(norm_in(x))), then
+    x <- x + norm_ff_out(feed_forward(norm_post(x))). Without a feed-forward the second step, its norms and their names
+    fall away."""
+    prefix: str
+    norm_in: Any
+    mixer: Any
+    norm_mix_out: Any
+    norm_post: Any
+    feed_forward: Any
+    norm_ff_out: Any
+    names: Tuple[Tuple[str, str], ...] = (("norm_in", "norm1."), ("mixer", "mix."), ("norm_mix_out", "norm1b."),
+                                          ("norm_post", "norm2."), ("feed_forward", "mlp."), ("norm_ff_out", "norm2b."))
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer. ``cache`` names the cache entry the layer's mixer uses; with
     ``writes=False`` the mixer only reads what the entry's owner stored in this step. Right before the
@@ -238,6 +299,7 @@ class ModelSpec:
     embed_scale: float = 1.0                   # multiplies the embedding row
     embed_position: Optional[Any] = None       # position spec whose vector is added to the embedding
     logit_cap: Optional[float] = None          # logits <- cap * tanh(logits / cap)
+    logit_scale: float = 1.0                   # multiplies the logits before the cap
     tables: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()   # learned float32 tables of the model itself: (checkpoint name, shape)
     extra: dict = field(default_factory=dict, compare=False)
 

@@ -650,11 +650,11 @@ def stream_add(h, other=None, vec=None):
     _check(lib, lib.dk_stream_add(_p(h), _p(other), _p(vec), c_longlong(h.shape[0]), h.shape[1], _stream()), "stream_add")
 
 
-def softcap(x, cap):
-    """x = cap * tanh(x / cap) in place (float32)."""
+def softcap(x, cap, factor=1.0):
+    """x = cap * tanh(factor * x / cap) in place (float32); without a cap (None or 0) x = factor * x."""
     _need(x, "x", torch.float32)
     lib = _lib("elementwise.cu")
-    _check(lib, lib.dk_softcap(_p(x), c_longlong(x.numel()), c_float(cap), _stream()), "softcap")
+    _check(lib, lib.dk_softcap(_p(x), c_longlong(x.numel()), c_float(cap or 0.0), c_float(factor), _stream()), "softcap")
 
 
 def xielu(z, out, alpha_pos, alpha_neg):
@@ -991,6 +991,23 @@ def scale_add_rmsnorm(h, alpha, delta, norm_w, eps, a_out):
                                          c_float(eps), h.shape[0], h.shape[1], _p(a_out), _stream()), "scale_add_rmsnorm")
 
 
+def normed_add_rmsnorm(h, delta, delta_w, delta_eps, norm_w, eps, a_out, rows=None):
+    """h += rmsnorm(delta) * delta_w (eps ``delta_eps``); a_out = rmsnorm(h) * norm_w. ``delta`` a tensor or a
+    ``Partial``. With ``rows`` (int32 indices) only those rows are worked out, into a_out[0..len(rows)), and h is
+    left unchanged."""
+    delta, parts, n_parts, stride = _parts(delta)
+    _need(h, "h", torch.float32, 2), _need(delta, "delta", a_out.dtype, 2), _need(norm_w, "norm_w", torch.float32, 1)
+    _need(delta_w, "delta_w", torch.float32, 1), _need(rows, "rows", torch.int32, 1), _need(a_out, "a_out", None, 2)
+    H = h.shape[1]
+    if norm_w.numel() != H or delta_w.numel() != H or (delta is not None and delta.shape != h.shape):
+        raise KernelError("normed_add_rmsnorm: shapes do not match")
+    n = h.shape[0] if rows is None else rows.numel()
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_normed_add_rmsnorm(_dt(a_out), _p(h), _p(delta), parts, n_parts, stride, _p(rows), _p(delta_w),
+                                          c_float(delta_eps), _p(norm_w), c_float(eps), n, H, _p(a_out), _stream()),
+           "normed_add_rmsnorm")
+
+
 def cast_rows(h, a_out):
     """a_out = h (float32) in a_out's type."""
     _need(h, "h", torch.float32, 2), _need(a_out, "a_out", None, 2)
@@ -1016,16 +1033,28 @@ def act_mul(gu, out, act):
 SHORT_CONV_MAX_TAPS = 9
 
 
+NORM_NONE, NORM_BEFORE_ROTATION, NORM_AFTER_ROTATION = 0, 1, 2
+
+
 def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos, sin, rot_dims, row_pos, row_seq, seq_pos0,
-                   seq_slot, n_heads, n_kv_heads, head_dim, v_head_dim, k_store=None, v_store=None, page_table=None):
+                   seq_slot, n_heads, n_kv_heads, head_dim, v_head_dim, k_store=None, v_store=None, page_table=None,
+                   norm_mode=None, v_mix=None, v_src=None):
     """Rows [q | k | v] of a fused projection -> ``out`` rows of the same layout: a causal convolution of
     ``taps`` taps over time on every channel (``w_conv`` [channels, taps]; earlier rows of the same step, or
     the sequence's ``state`` [slots, taps-1, channels] for positions before it), then per q and k head an RMS
     norm with weights of the head's size, then the rotate-half rotation of the first ``rot_dims`` coordinates
-    by cos/sin [positions, rot_dims/2]. Each step optional (taps 1, weights None, rot_dims 0). The state is
+    by cos/sin [positions, rot_dims/2]. Each step optional (taps 1, weights None, rot_dims 0). ``norm_mode``: by
+    default the norm runs before the rotation when weights are given; ``NORM_AFTER_ROTATION`` puts it behind, and with
+    either mode and no weights the heads are divided by their root mean square alone. ``v_src`` (rows of v heads, the
+    projection's type) with ``v_mix`` (float32, one number): v <- (1 - v_mix) v + v_mix v_src. The state is
     only read: ``conv_state_update`` moves it on afterwards. With ``k_store`` / ``v_store`` [pages, nkv, PAGE, size] and
     ``page_table`` the k and v heads also go to each token's place in the paged cache."""
-    _need_rows(proj, "proj"), _need_rows(out, "out", proj.dtype)
+    _need_rows(proj, "proj"), _need_rows(out, "out", proj.dtype), _need_rows(v_src, "v_src", proj.dtype)
+    if norm_mode is None:
+        norm_mode = NORM_BEFORE_ROTATION if q_norm_w is not None else NORM_NONE
+    if (v_src is None) != (v_mix is None) or (v_src is not None and (v_src.shape != (proj.shape[0], n_kv_heads * v_head_dim)
+                                                                     or v_mix.numel() != 1 or v_mix.dtype != torch.float32)):
+        raise KernelError("conv_norm_rope: v_src [tokens, nkv * hdv] and v_mix (one float32) come together")
     C = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
     _need(state, "state", proj.dtype, 3), _need(w_conv, "w_conv", proj.dtype, 2)
     _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
@@ -1044,7 +1073,8 @@ def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos,
             raise KernelError("conv_norm_rope: key/value stores of the wrong shape")
     lib = _lib("short_conv.cu")
     _check(lib, lib.dk_conv_norm_rope(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(out), c_longlong(out.stride(0)),
-                                      _p(state), _p(w_conv), int(taps), _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos),
+                                      _p(state), _p(w_conv), int(taps), int(norm_mode), _p(q_norm_w), _p(k_norm_w),
+                                      c_float(eps), _p(v_mix), _p(v_src), c_longlong(v_src.stride(0) if v_src is not None else 0), _p(cos),
                                       _p(sin), int(rot_dims), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot),
                                       proj.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, _p(k_store), _p(v_store),
                                       _p(page_table), page_table.shape[1] if page_table is not None else 0, _stream()),
@@ -1061,6 +1091,62 @@ def conv_state_update(proj, state, taps, cu_q, seq_pos0, seq_slot, n_seq):
     lib = _lib("short_conv.cu")
     _check(lib, lib.dk_conv_state_update(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(state), int(taps), proj.shape[1],
                                          _p(cu_q), _p(seq_pos0), _p(seq_slot), n_seq, _stream()), "conv_state_update")
+
+
+# ------------------------------------------------------------------- attention through low-rank latents
+def latent_norm_rope_write(proj, cq_out, q_norm_w, kv_norm_w, eps, cos, sin, rot_dims, row_pos, row_seq, q_rank, kv_rank,
+                           rot_dim, k_store=None, v_store=None, page_table=None):
+    """Rows [a (q_rank) | b (kv_rank) | r (rot_dim)] of a fused down projection: cq_out = rmsnorm(a) * q_norm_w;
+    rmsnorm(b) * kv_norm_w and r, its first ``rot_dims`` coordinates rotated by neighbouring pairs (cos/sin
+    [positions, rot_dims/2]), go to each token's place in the paged cache of one kv head: key row [c | r]
+    (k_store [pages, 1, PAGE, kv_rank + rot_dim]), value row c (v_store [pages, 1, PAGE, kv_rank])."""
+    _need_rows(proj, "proj"), _need_rows(cq_out, "cq_out", proj.dtype)
+    _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(kv_norm_w, "kv_norm_w", torch.float32, 1)
+    _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    if proj.shape[1] != q_rank + kv_rank + rot_dim or cq_out.shape != (proj.shape[0], q_rank) or q_norm_w.numel() != q_rank \
+            or kv_norm_w.numel() != kv_rank or rot_dims % 2 or rot_dims > rot_dim or \
+            (rot_dims and (cos is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape)):
+        raise KernelError("latent_norm_rope_write: shapes do not match")
+    if k_store is not None:
+        _need(k_store, "k_store", proj.dtype, 4), _need(v_store, "v_store", proj.dtype, 4), _need(page_table, "page_table", torch.int32, 2)
+        if k_store.shape[1:] != (1, PAGE, kv_rank + rot_dim) or v_store.shape[1:] != (1, PAGE, kv_rank):
+            raise KernelError("latent_norm_rope_write: key/value stores of the wrong shape")
+    lib = _lib("latent.cu")
+    _check(lib, lib.dk_latent_norm_rope_write(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(cq_out), c_longlong(cq_out.stride(0)),
+                                              _p(q_norm_w), _p(kv_norm_w), c_float(eps), _p(cos), _p(sin), int(rot_dims),
+                                              _p(row_pos), _p(row_seq), proj.shape[0], q_rank, kv_rank, rot_dim, _p(k_store),
+                                              _p(v_store), _p(page_table), page_table.shape[1] if page_table is not None else 0,
+                                              _stream()), "latent_norm_rope_write")
+
+
+def latent_query(q, w_uk, out, cos, sin, rot_dims, row_pos, n_heads, dim, rot_dim, kv_rank, plain=True):
+    """q [tokens, heads * (dim + rot_dim)], head by head [plain | rot] -> out [tokens, heads * (kv_rank + rot_dim)],
+    head by head [W_uk_h^T plain | rot rotated by neighbouring pairs], with w_uk [heads * dim, kv_rank]. Rows with
+    position < 0 become zeros. ``plain=False``: only the rotated parts are written (the plain parts come from a
+    product of the caller's)."""
+    _need_rows(q, "q"), _need_rows(out, "out", q.dtype), _need(w_uk, "w_uk", q.dtype, 2)
+    _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2), _need(row_pos, "row_pos", torch.int32, 1)
+    if q.shape[1] != n_heads * (dim + rot_dim) or out.shape != (q.shape[0], n_heads * (kv_rank + rot_dim)) or \
+            tuple(w_uk.shape) != (n_heads * dim, kv_rank) or rot_dims % 2 or rot_dims > rot_dim or \
+            (rot_dims and (cos is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape)):
+        raise KernelError("latent_query: shapes do not match")
+    lib = _lib("latent.cu")
+    _check(lib, lib.dk_latent_query(_dt(q), _p(q), c_longlong(q.stride(0)), _p(w_uk), _p(out), c_longlong(out.stride(0)), _p(cos),
+                                    _p(sin), int(rot_dims), _p(row_pos), q.shape[0], n_heads, dim, rot_dim, kv_rank,
+                                    int(bool(plain)), _stream()), "latent_query")
+
+
+def latent_value(o_lat, w_uv, out, n_heads, kv_rank, vdim):
+    """o_lat [tokens, heads * kv_rank] -> out [tokens, heads * vdim]: head h's row times w_uv[h * vdim : (h + 1) * vdim]
+    ([heads * vdim, kv_rank])."""
+    _need_rows(o_lat, "o_lat"), _need_rows(out, "out", o_lat.dtype), _need(w_uv, "w_uv", o_lat.dtype, 2)
+    if o_lat.shape[1] != n_heads * kv_rank or out.shape != (o_lat.shape[0], n_heads * vdim) or \
+            tuple(w_uv.shape) != (n_heads * vdim, kv_rank):
+        raise KernelError("latent_value: shapes do not match")
+    lib = _lib("latent.cu")
+    _check(lib, lib.dk_latent_value(_dt(o_lat), _p(o_lat), c_longlong(o_lat.stride(0)), _p(w_uv), _p(out),
+                                    c_longlong(out.stride(0)), o_lat.shape[0], n_heads, kv_rank, vdim, _stream()), "latent_value")
 
 
 # ------------------------------------------------------------------------------ mixture of experts

@@ -643,16 +643,19 @@ DK_EXPORT int dk_stream_add(float* h, const float* other, const float* vec, long
     return dk_launch(stream_add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, h, other, vec, n, H);
 }
 
-// x = cap * tanh(x / cap) in place (float32 logits)
-__global__ void softcap_kernel(float* x, size_t n, float cap) {
+// x = cap * tanh(factor * x / cap) in place (float32 logits); cap 0: x = factor * x
+__global__ void softcap_kernel(float* x, size_t n, float cap, float factor) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+    if (i < n) {
+        const float v = x[i] * factor;
+        x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+    }
 }
 
-DK_EXPORT int dk_softcap(float* x, long long n, float cap, cudaStream_t st) {
-    return dk_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, (size_t)n, cap);
+DK_EXPORT int dk_softcap(float* x, long long n, float cap, float factor, cudaStream_t st) {
+    return dk_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, (size_t)n, cap, factor);
 }
 
 // xIELU (common.cuh) as a kernel of its own, for the products that do not have it in their epilogue.
@@ -782,6 +785,128 @@ DK_EXPORT int dk_scale_add_rmsnorm(int dtype, float* h, float alpha, const void*
     }
     DISPATCH_T(dtype, return dk_launch(scale_add_rmsnorm_kernel<T>, dim3(n_rows), dim3(row_threads(H)), 0, st, h, alpha,
                                        (const T*)delta, parts, n_parts, (size_t)part_stride, w, eps, H, (T*)a));
+}
+
+// ---------------------------------------------------------------------------------------------
+// A sublayer's output normed before it joins the stream, and the next norm behind the sum:
+//   h[row] += rmsnorm(delta[row]) * wb (eps_b);   a[out_row] = rmsnorm(h[row]) * w (eps).
+// delta as a tensor or as n_parts float32 partial sums. With `rows` the kernel gathers (out_row = blockIdx.x,
+// row = rows[blockIdx.x]) and leaves h as it is. Sums, mean squares and scalings are float32.
+// The generic form keeps the row in shared memory (H floats); any width.
+template <typename T>
+__global__ void normed_add_rmsnorm_kernel(float* h, const T* delta, const float* parts, int n_parts, size_t part_stride,
+                                          const int* rows, const float* __restrict__ wb, float eps_b,
+                                          const float* __restrict__ w, float eps, int H, T* a) {
+    __shared__ float red[33];
+    extern __shared__ float vals[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t out_row = blockIdx.x;
+    const size_t row = rows ? (size_t)rows[out_row] : out_row;
+    float* hr = h + row * H;
+    float ssd = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float d = delta ? to_f(delta[row * H + i]) : 0.f;
+        for (int k = 0; k < n_parts; k++) d += parts[(size_t)k * part_stride + row * H + i];
+        vals[i] = d;
+        ssd += d * d;
+    }
+    ssd = block_sum(ssd, red);
+    const float rd = 1.f / sqrtf(ssd / (float)H + eps_b);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = hr[i] + vals[i] * rd * wb[i];
+        vals[i] = v;
+        if (!rows) hr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.f / sqrtf(ss / (float)H + eps);
+    T* ar = a + out_row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(vals[i] * rs * w[i]);
+}
+
+// The same in one pass for widths that are multiples of 4 up to 8,192: NV groups of 4 columns a thread stay in
+// registers between the two sums of squares and the scaling; both weights are fetched before the wait.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+normed_add_rmsnorm_regs_kernel(float* h, const T* delta, const float* parts, int n_parts, size_t part_stride,
+                               const int* rows, const float* __restrict__ wb, float eps_b, const float* __restrict__ w,
+                               float eps, int H, T* a) {
+    __shared__ float red[33];
+    float4 wv[NV], wbv[NV], v[NV], d[NV];
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        const int c = (threadIdx.x + q * 256) * 4;
+        wv[q] = c < H ? ld4(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        wbv[q] = c < H ? ld4(wb + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t out_row = blockIdx.x;
+    const size_t row = rows ? (size_t)rows[out_row] : out_row;
+    float* hr = h + row * H;
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        const int c = (threadIdx.x + q * 256) * 4;
+        v[q] = c < H ? ld4(hr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        d[q] = (c < H && delta) ? ld4(delta + row * H + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int k = 0; k < n_parts; k++)
+#pragma unroll
+        for (int q = 0; q < NV; q++) {
+            const int c = (threadIdx.x + q * 256) * 4;
+            if (c < H) {
+                const float4 p = ld4(parts + (size_t)k * part_stride + row * H + c);
+                d[q].x += p.x, d[q].y += p.y, d[q].z += p.z, d[q].w += p.w;
+            }
+        }
+    float ssd = 0.f;
+#pragma unroll
+    for (int q = 0; q < NV; q++) ssd += d[q].x * d[q].x + d[q].y * d[q].y + d[q].z * d[q].z + d[q].w * d[q].w;
+    ssd = block_sum(ssd, red);
+    const float rd = 1.f / sqrtf(ssd / (float)H + eps_b);
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        v[q].x += d[q].x * rd * wbv[q].x, v[q].y += d[q].y * rd * wbv[q].y;
+        v[q].z += d[q].z * rd * wbv[q].z, v[q].w += d[q].w * rd * wbv[q].w;
+        ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        const int c = (threadIdx.x + q * 256) * 4;
+        if (c < H) {
+            if (!rows) st4(hr + c, v[q]);
+            st4(a + out_row * H + c, make_float4(v[q].x * rs * wv[q].x, v[q].y * rs * wv[q].y, v[q].z * rs * wv[q].z,
+                                                 v[q].w * rs * wv[q].w));
+        }
+    }
+}
+
+DK_EXPORT int dk_normed_add_rmsnorm(int dtype, float* h, const void* delta, const float* parts, int n_parts,
+                                    long long part_stride, const int* rows, const float* wb, float eps_b, const float* w,
+                                    float eps, int n_rows, int H, void* a, cudaStream_t st) {
+    if (H % 4 == 0 && H <= 8192 && part_stride % 4 == 0) {
+#define NAN_REGS(NV)                                                                                                       \
+    if (H <= 1024 * NV) {                                                                                                  \
+        DISPATCH_T(dtype, return dk_launch(normed_add_rmsnorm_regs_kernel<T, NV>, dim3(n_rows), dim3(256), 0, st, h,       \
+                                           (const T*)delta, parts, n_parts, (size_t)part_stride, rows, wb, eps_b, w, eps,  \
+                                           H, (T*)a));                                                                     \
+    }
+        NAN_REGS(1) NAN_REGS(2) NAN_REGS(3) NAN_REGS(4) NAN_REGS(6) NAN_REGS(8)
+#undef NAN_REGS
+    }
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024) {
+        DISPATCH_T(dtype, cudaFuncSetAttribute(normed_add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem));
+    }
+    DISPATCH_T(dtype, return dk_launch(normed_add_rmsnorm_kernel<T>, dim3(n_rows), dim3(row_threads(H)), smem, st, h,
+                                       (const T*)delta, parts, n_parts, (size_t)part_stride, rows, wb, eps_b, w, eps, H,
+                                       (T*)a));
 }
 
 // a[row] = h[row] in the storage type (the stream as a sublayer's input, where no kernel before left it).

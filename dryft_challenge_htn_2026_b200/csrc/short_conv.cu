@@ -3,10 +3,13 @@
 //       y_t[c] = sum_j w[c][j] * u_(t - taps + 1 + j)[c],   zeros before the sequence's start,
 //     whose memory, the last taps - 1 projected rows of each sequence, is a per-sequence state
 //     [slots, taps - 1, channels] (zero when a slot is taken, so that the zeros come by themselves);
-//   * an RMS norm over each query and key head with a weight of the head's size,
+//   * an RMS norm over each query and key head, with a weight of the head's size or without one, before the
+//     rotation (norm_mode 1) or after it (norm_mode 2),
 //   * a rotate-half rotation of the first rot_dims coordinates of each query and key head (coordinate i
-//     with i + rot_dims / 2) by angles from a table [positions, rot_dims / 2]; the rest pass.
-// Each option may be left out (taps = 1, no norm weights, rot_dims = 0). The result is a dense row
+//     with i + rot_dims / 2) by angles from a table [positions, rot_dims / 2]; the rest pass,
+//   * values blended with another layer's values of the same token: v <- (1 - lam) v + lam v_src, lam a
+//     learned number on the device.
+// Each option may be left out (taps = 1, norm_mode 0, rot_dims = 0, no v_src). The result is a dense row
 // [q heads | k heads | v heads] in the storage type; sums, norms and the rotation are float32. Given the paged
 // key and value stores, the kernel also writes each token's k and v heads to their place there (the step's cache write).
 // A second kernel moves the state on once the first has read it.
@@ -19,7 +22,8 @@
 template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
 conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const T* state, const T* __restrict__ wconv,
-                      int taps, const float* __restrict__ qn, const float* __restrict__ kn, float eps,
+                      int taps, int norm_mode, const float* __restrict__ qn, const float* __restrict__ kn, float eps,
+                      const float* __restrict__ vmix, const T* v_src, long long ld_src,
                       const float* __restrict__ cosv, const float* __restrict__ sinv, int rot_dims, const int* row_pos,
                       const int* row_seq, const int* seq_pos0, const int* seq_slot, int nh, int nkv, int hd, int hdv,
                       T* k_store, T* v_store, const int* page_table, int pt_stride) {
@@ -39,6 +43,7 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
     else if (head < nh + nkv) { c0 = nh * hd + (head - nh) * hd; size = hd; wn = kn; }
     else { c0 = (nh + nkv) * hd + (head - nh - nkv) * hdv; size = hdv; }
     const bool rotates = head < nh + nkv && rot_dims > 0;
+    const bool norms = head < nh + nkv && norm_mode != 0;
     const T* st = taps > 1 ? state + (size_t)seq_slot[s] * (taps - 1) * C : nullptr;
     float y[2];
     float ss = 0.f;
@@ -61,13 +66,24 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
             ss += acc * acc;
         }
     }
-    if (wn != nullptr) {
-        ss = block_sum(ss, red);
-        const float rs = 1.f / sqrtf(ss / (float)size + eps);
+    if (norms) {     // the rotation turns pairs of coordinates and leaves the sum of squares as it is up to rounding; the
+                     // norm behind it is taken of the rotated numbers all the same (below)
+        if (norm_mode == 1) {
+            ss = block_sum(ss, red);
+            const float rs = 1.f / sqrtf(ss / (float)size + eps);
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int d = threadIdx.x + r * SC_THREADS;
+                if (d < size) y[r] *= wn ? rs * wn[d] : rs;
+            }
+        }
+    } else if (head >= nh + nkv && v_src != nullptr) {
+        const float lam = vmix[0];
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             const int d = threadIdx.x + r * SC_THREADS;
-            if (d < size) y[r] *= rs * wn[d];
+            if (d < size)
+                y[r] = (1.f - lam) * y[r] + lam * to_f(v_src[(size_t)t * ld_src + (size_t)(head - nh - nkv) * hdv + d]);
         }
     }
     if (rotates) {
@@ -86,6 +102,21 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
                 const float c = cosv[(size_t)pos * half + i], sn = sinv[(size_t)pos * half + i];
                 y[r] = d < half ? ys[d] * c - ys[d + half] * sn : ys[d] * c + ys[d - half] * sn;
             }
+        }
+    }
+    if (norms && norm_mode == 2) {
+        ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int d = threadIdx.x + r * SC_THREADS;
+            if (d < size) ss += y[r] * y[r];
+        }
+        ss = block_sum(ss, red);
+        const float rs = 1.f / sqrtf(ss / (float)size + eps);
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int d = threadIdx.x + r * SC_THREADS;
+            if (d < size) y[r] *= wn ? rs * wn[d] : rs;
         }
     }
     // k and v heads also go to the token's place in the paged stores when those are given (the cache write of the step)
@@ -133,8 +164,8 @@ __global__ void conv_state_update_kernel(const T* proj, long long ld, T* state, 
 }
 
 DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void* out, long long ldo, const void* state,
-                                const void* wconv, int taps, const float* qn, const float* kn, float eps,
-                                const float* cosv, const float* sinv, int rot_dims, const int* row_pos,
+                                const void* wconv, int taps, int norm_mode, const float* qn, const float* kn, float eps,
+                                const float* vmix, const void* v_src, long long ld_src, const float* cosv, const float* sinv, int rot_dims, const int* row_pos,
                                 const int* row_seq, const int* seq_pos0, const int* seq_slot, int n_tok, int nh, int nkv,
                                 int hd, int hdv, void* k_store, void* v_store, const int* page_table, int pt_stride,
                                 cudaStream_t st) {
@@ -143,10 +174,10 @@ DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void*
     const dim3 grid(n_tok, nh + 2 * nkv), block(SC_THREADS);
     if (dtype == 0)
         return dk_launch(conv_norm_rope_kernel<float>, grid, block, 0, st, (const float*)proj, ld, (float*)out, ldo,
-                         (const float*)state, (const float*)wconv, taps, qn, kn, eps, cosv, sinv, rot_dims, row_pos,
+                         (const float*)state, (const float*)wconv, taps, norm_mode, qn, kn, eps, vmix, (const float*)v_src, ld_src, cosv, sinv, rot_dims, row_pos,
                          row_seq, seq_pos0, seq_slot, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride);
     return dk_launch(conv_norm_rope_kernel<bf16>, grid, block, 0, st, (const bf16*)proj, ld, (bf16*)out, ldo,
-                     (const bf16*)state, (const bf16*)wconv, taps, qn, kn, eps, cosv, sinv, rot_dims, row_pos, row_seq,
+                     (const bf16*)state, (const bf16*)wconv, taps, norm_mode, qn, kn, eps, vmix, (const bf16*)v_src, ld_src, cosv, sinv, rot_dims, row_pos, row_seq,
                      seq_pos0, seq_slot, nh, nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride);
 }
 

@@ -112,6 +112,7 @@ class CausalLM:
         # the embedding kernel computes RMSNorm and nothing else, and only of the embedding as it leaves the kernel
         fused = isinstance(getattr(first, "norm_in", None), RMSNorm) and not (s.schedule[0].add_embedding or s.schedule[0].add_row)
         norm_w, eps = (first.norm_in.weight, first.norm_in.spec.eps) if fused else (None, 0.0)
+        ctx.carry = {}           # what one layer of the step leaves for later ones (e.g. values that layers share)
         ctx.stream_copy = None   # the stream in the storage type, where a kernel has left it (blocks with the norm after the sum)
         plain = getattr(first, "reads_stream", False) and not (s.schedule[0].add_embedding or s.schedule[0].add_row)
         if self.position is None and s.embed_scale == 1.0:
@@ -132,11 +133,12 @@ class CausalLM:
                                                    a if (i == 0 and fused) else None)
             if tap is not None:
                 tap(i, h.clone() if pending is None else
-                    h + (pending.ws.sum(0) if isinstance(pending, api.Partial) else pending.to(torch.float32)))
+                    h + (pending.to_float32() if hasattr(pending, "to_float32") else
+                         pending.ws.sum(0) if isinstance(pending, api.Partial) else pending.to(torch.float32)))
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
         an = add_norm(self.final_norm, h, pending, rt.dtype, rows=ctx.want_rows)
         logits = linear(an, self.head, STORE_F32)
-        if s.logit_cap:
-            api.softcap(logits, s.logit_cap)
+        if s.logit_cap or s.logit_scale != 1.0:
+            api.softcap(logits, s.logit_cap, s.logit_scale)
         return logits

@@ -15,7 +15,7 @@ the projected rows and leaves scale * (gated heads) where the caller wants them.
 import torch
 
 from ..cache.requests import KVRequest, StateRequest
-from ..config.specs import MaskedAttentionSpec
+from ..config.specs import MaskedAttentionSpec, UnitRMSNormSpec
 from ..csrc import api
 from .attention import QueryTiles
 from .base import ParamDecl, Part, build_part, register_part
@@ -47,10 +47,13 @@ class MaskedAttention(Part):
         if not 1 <= self.taps <= api.SHORT_CONV_MAX_TAPS:
             raise ValueError(f"a convolution of {s.conv_taps} taps (1 to {api.SHORT_CONV_MAX_TAPS})")
         self.qk_norm = s.qk_norm
+        self.qk_norm_weights = s.qk_norm is not None and not isinstance(s.qk_norm, UnitRMSNormSpec)
+        if s.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"value_mix {s.value_mix!r} (source, blend or none)")
         self.position = build_part(s.position, rt) if s.position is not None else None
         if self.position is not None and self.position.spec.dim > s.head_dim:
             raise ValueError(f"a rotation over {self.position.spec.dim} coordinates of heads of {s.head_dim}")
-        self.prepares = self.taps > 1 or self.qk_norm is not None or self.position is not None
+        self.prepares = self.taps > 1 or self.qk_norm is not None or self.position is not None or s.value_mix is not None
         self.n_qkv = self.n_q + self.n_k + self.n_v
         self.q_norm_w = self.k_norm_w = self.w_conv = None
         self.max_positions = 0
@@ -82,9 +85,11 @@ class MaskedAttention(Part):
         if self.taps > 1:
             d += [ParamDecl("q.conv", (self.n_q, self.taps), init="taps"), ParamDecl("k.conv", (self.n_k, self.taps), init="taps"),
                   ParamDecl("v.conv", (self.n_v, self.taps), init="taps")]
-        if self.qk_norm is not None:
+        if self.qk_norm_weights:
             d += [ParamDecl("q.norm", (s.head_dim,), init="norm", keep_float32=True),
                   ParamDecl("k.norm", (s.head_dim,), init="norm", keep_float32=True)]
+        if s.value_mix is not None:
+            d.append(ParamDecl("vmix", (), init="fraction", keep_float32=True))
         return d
 
     def bind(self, tensors):
@@ -100,9 +105,11 @@ class MaskedAttention(Part):
             self.sink = tensors.pop("sink").to(torch.float32).contiguous()
         if self.taps > 1:
             self.w_conv = torch.cat([tensors.pop("q.conv"), tensors.pop("k.conv"), tensors.pop("v.conv")], 0).contiguous()
-        if self.qk_norm is not None:
+        if self.qk_norm_weights:
             self.q_norm_w = tensors.pop("q.norm").to(torch.float32).contiguous()
             self.k_norm_w = tensors.pop("k.norm").to(torch.float32).contiguous()
+        if self.spec.value_mix is not None:
+            self.v_mix = tensors.pop("vmix").to(torch.float32).reshape(1).contiguous()
 
     def step_weights(self):
         return [self.w_in, self.w_o]
@@ -134,11 +141,21 @@ class MaskedAttention(Part):
             cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1))
         pos0 = ctx.row_pos if ctx.is_decode else ctx.seq_pos0     # one token a row: its position is what came before
         qkv = proj[:, :self.n_qkv]
+        norm_mode = api.NORM_NONE if self.qk_norm is None else \
+            api.NORM_AFTER_ROTATION if s.norm_after_rotation else api.NORM_BEFORE_ROTATION
+        v_src = None
+        if s.value_mix == "blend":
+            v_src = ctx.carry.get(("value_mix", self.n_v))
+            if v_src is None:
+                raise ValueError("a layer blends its values with a source layer's, but none ran before it in this step")
         api.conv_norm_rope(qkv, out, state, self.w_conv, self.taps, self.q_norm_w, self.k_norm_w,
                            self.qk_norm.eps if self.qk_norm is not None else 0.0, cos, sin, rot, ctx.row_pos, ctx.row_seq,
                            pos0, ctx.seq_slot, s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim,
                            views[0].k if writes else None, views[0].v if writes else None,
-                           ctx.tables[views[0].group] if writes else None)
+                           ctx.tables[views[0].group] if writes else None, norm_mode=norm_mode,
+                           v_mix=self.v_mix if v_src is not None else None, v_src=v_src)
+        if s.value_mix == "source":      # this step's values, for the layers that blend theirs with them
+            ctx.carry[("value_mix", self.n_v)] = out[:, self.n_q + self.n_k:]
         if self.taps > 1:
             api.conv_state_update(qkv, state, self.taps, None if ctx.is_decode else ctx.cu_q, pos0, ctx.seq_slot, ctx.n_seq)
         return out
@@ -147,7 +164,6 @@ class MaskedAttention(Part):
         """``proj`` [tokens, n_in]: this part's rows of a projection (possibly columns of a wider matrix);
         ``mid`` [tokens, n_mid]: where scale * (gated heads) go."""
         s, kv = self.spec, views[0]
-        table = ctx.tables[kv.group]
         gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
         if self.prepares:
             proj = self.prepared_rows(ctx, views, proj, writes)
@@ -155,6 +171,13 @@ class MaskedAttention(Part):
         q = proj[:, :self.n_q]
         k = proj[:, self.n_q:self.n_q + self.n_k]
         v = proj[:, self.n_q + self.n_k:self.n_q + self.n_k + self.n_v]
+        return self.attend(ctx, kv, q, k, v, gate, mid, scale, writes)
+
+    def attend(self, ctx, kv, q, k, v, gate, mid, scale, writes=True):
+        """Attention of the query rows ``q`` over the cache entry ``kv``, into ``mid``; with ``writes`` the step's
+        ``k`` and ``v`` rows go into the cache first. Picks the kernel by type, phase and head sizes."""
+        s = self.spec
+        table = ctx.tables[kv.group]
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
         if self.tensor_core and ctx.is_decode and api.masked_decode_streams(q, mid, gate, s.head_dim, s.v_head_dim):
             # single tokens, keys and values of one size: the library's split decode kernel in its masked build

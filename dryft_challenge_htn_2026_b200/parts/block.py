@@ -8,9 +8,10 @@ norm that says ``takes_partial`` adds them up while it reads, for any other they
 """
 import torch
 
-from ..config.specs import LayerSpec, PostNormLayerSpec
+from ..config.specs import LayerSpec, PostNormLayerSpec, SandwichLayerSpec
 from ..csrc import api
 from .base import ParamDecl, Part, build_part, register_part
+from .norm import NormedDelta, RMSNorm
 
 
 class PreNormBlock(Part):
@@ -61,6 +62,8 @@ class PreNormBlock(Part):
 
 def add_norm(norm, h, delta, dtype, rows=None):
     """h += delta, then norm(h) (of the rows ``rows`` only, leaving h alone, when given)."""
+    if isinstance(delta, NormedDelta) and not isinstance(norm, RMSNorm):
+        raise TypeError(f"{type(norm).__name__} cannot follow a sublayer whose output has a norm of its own")
     if isinstance(delta, api.Partial) and not getattr(norm, "takes_partial", False):
         delta = delta.sum(dtype)
     n = h.shape[0] if rows is None else rows.numel()
@@ -99,6 +102,8 @@ class PostNormBlock(Part):
     def forward(self, ctx, h, pending, views, writes=True, a=None):
         dtype = self.rt.dtype
         if pending is not None:          # a block before this one left its output to be added
+            if isinstance(pending, NormedDelta):
+                pending = pending.to_float32()
             if isinstance(pending, api.Partial):
                 pending = pending.sum(dtype)
             api.stream_add(h, pending.to(torch.float32))
@@ -118,3 +123,34 @@ class PostNormBlock(Part):
 
 
 register_part(PostNormLayerSpec, PostNormBlock)
+
+
+class SandwichBlock(PreNormBlock):
+    """A norm before and after each sublayer: h += norm_mix_out(mixer(norm_in(h))); h += norm_ff_out(feed_forward(
+    norm_post(h))). Like the pre-norm block it takes the block before's output as ``pending`` and hands its own on, as
+    a ``NormedDelta``: the norm of a sublayer's output, the sum and the norm behind the sum are one kernel."""
+
+    def __init__(self, spec, rt):
+        Part.__init__(self, spec, rt)
+        self.norm_in = build_part(spec.norm_in, rt)
+        self.mixer = build_part(spec.mixer, rt)
+        self.norm_mix_out = build_part(spec.norm_mix_out, rt)
+        has_ff = spec.feed_forward is not None
+        self.norm_post = build_part(spec.norm_post, rt) if has_ff else None
+        self.feed_forward = build_part(spec.feed_forward, rt) if has_ff else None
+        self.norm_ff_out = build_part(spec.norm_ff_out, rt) if has_ff else None
+        for n in (self.norm_in, self.norm_mix_out, self.norm_post, self.norm_ff_out):
+            if n is not None and not isinstance(n, RMSNorm):
+                raise TypeError(f"{type(n).__name__}: the norms around a sublayer run on the RMS norm's kernels")
+
+    def forward(self, ctx, h, pending, views, writes=True, a=None):
+        if a is None:
+            a = add_norm(self.norm_in, h, pending, self.rt.dtype)
+        d = NormedDelta(self.mixer.forward(ctx, views, a, writes), self.norm_mix_out)
+        if self.feed_forward is None:
+            return d
+        a = add_norm(self.norm_post, h, d, self.rt.dtype)
+        return NormedDelta(self.feed_forward.forward(ctx, a), self.norm_ff_out)
+
+
+register_part(SandwichLayerSpec, SandwichBlock)

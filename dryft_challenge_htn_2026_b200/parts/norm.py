@@ -6,20 +6,38 @@ from ..csrc import api
 from .base import ParamDecl, Part, register_part
 
 
+class NormedDelta:
+    """A sublayer's output that still has to go through a norm of its own before it joins the residual stream:
+    ``delta`` (a tensor or a ``csrc.api.Partial``) and ``norm`` (an ``RMSNorm`` part). The norm that follows the sum
+    takes it as its ``delta`` and does both in one kernel."""
+
+    def __init__(self, delta, norm):
+        self.delta, self.norm = delta, norm
+
+    def to_float32(self):
+        """What joins the stream, worked out plainly (for dumps of the stream between layers)."""
+        d = self.delta.ws.sum(0) if isinstance(self.delta, api.Partial) else self.delta.to(torch.float32)
+        return d * torch.rsqrt((d * d).mean(-1, keepdim=True) + self.norm.spec.eps) * self.norm.weight
+
+
 class RMSNorm(Part):
     """y = w * x * rsqrt(mean(x^2) + eps), statistics in float32, weight held in float32."""
     takes_partial = True     # add_forward adds up split-K partial sums (csrc.api.Partial) while it reads them
 
     def param_decls(self):
-        return [ParamDecl("weight", (self.spec.dim,), init="norm", keep_float32=True)]
+        return [ParamDecl(self.spec.tensor, (self.spec.dim,), init="norm", keep_float32=True)]
 
     def bind(self, tensors):
-        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.weight = tensors[self.spec.tensor].to(torch.float32).contiguous()
 
     def add_forward(self, h, delta, out, rows=None):
-        """h (float32 residual stream) += delta (a tensor, a ``csrc.api.Partial`` or None);
-        out = norm(h). ``rows``: only these rows, into out[0..len(rows)), leaving h as it is."""
-        api.add_rmsnorm(h, delta, self.weight, self.spec.eps, out, rows)
+        """h (float32 residual stream) += delta (a tensor, a ``csrc.api.Partial`` or None; a ``NormedDelta`` goes
+        through its own norm first); out = norm(h). ``rows``: only these rows, into out[0..len(rows)), leaving h as
+        it is."""
+        if isinstance(delta, NormedDelta):
+            api.normed_add_rmsnorm(h, delta.delta, delta.norm.weight, delta.norm.spec.eps, self.weight, self.spec.eps, out, rows)
+        else:
+            api.add_rmsnorm(h, delta, self.weight, self.spec.eps, out, rows)
         return out
 
     def scale_add_forward(self, h, alpha, delta, out):

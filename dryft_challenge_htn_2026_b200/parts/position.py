@@ -10,7 +10,7 @@ cache write and cannot be combined with a per-head q/k norm (which would have to
 attention part refuses that pair."""
 import torch
 
-from ..config.specs import RotaryHalfSpec, RotaryPartSpec, SinusoidSpec
+from ..config.specs import RotaryHalfSpec, RotaryPairsSpec, RotaryPartSpec, SinusoidSpec
 from .base import Part, register_part
 
 
@@ -80,3 +80,12 @@ class RotaryPart(Part):
 
 
 register_part(RotaryPartSpec, RotaryPart)
+
+
+class RotaryPairs(RotaryPart):
+    """The same angle tables for a rotation of neighbouring pairs (coordinate 2i with 2i + 1) over the first ``dim``
+    coordinates; the kernel of the mixer that owns the part turns the pairs."""
+    pairs = True
+
+
+register_part(RotaryPairsSpec, RotaryPairs)

@@ -7,6 +7,7 @@ from .config.base import ConfigError, read_config_json
 from .config.nilivik import NilivikConfig
 from .config.pibulix import PibulixConfig
 from .config.qwen3 import Qwen3Config
+from .config.venidra import VenidraConfig
 
 _ARCHITECTURES = {}
 
@@ -45,3 +46,4 @@ def config_from_folder(folder):
 register_architecture(Qwen3Config)
 register_architecture(NilivikConfig)
 register_architecture(PibulixConfig)
+register_architecture(VenidraConfig)

@@ -24,6 +24,8 @@ def _shape_draw(x, init, matrix_std, norm_std):
         return norm_std * x
     if init == "taps":              # a short convolution's taps: of the order of one
         return 0.5 * x
+    if init == "fraction":          # a blending weight between 0 and 1
+        return torch.sigmoid(x)
     if init == "wide":              # matrices whose outputs should spread (routers, the second step of a decay)
         return 10.0 * matrix_std * x
     return matrix_std * x
