@@ -301,6 +301,7 @@ class ModelSpec:
     logit_cap: Optional[float] = None          # logits <- cap * tanh(logits / cap)
     logit_scale: float = 1.0                   # multiplies the logits before the cap
     tables: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()   # learned float32 tables of the model itself: (checkpoint name, shape)
+    unused_tensors: Tuple[str, ...] = ()       # checkpoint names the design ships although nothing reads them
     extra: dict = field(default_factory=dict, compare=False)
 
     @staticmethod

@@ -164,4 +164,7 @@ class VenidraConfig(ModelConfig):
                          schedule=ModelSpec.identity_schedule(len(layers)), final_norm=RMSNormSpec(W, eps, tensor=""),
                          tie_embeddings=True, max_positions=1 << 20, embed_name="embed", final_norm_prefix="final.norm",
                          head_name="head", embed_scale=self.embedding_scale, logit_cap=self.logit_softcap or None,
-                         logit_scale=self.logit_scale)
+                         logit_scale=self.logit_scale,
+                         # a blending weight may come with an attention layer that does not blend: nothing reads it
+                         unused_tensors=tuple(f"l{i}.mix.vmix" for i, lc in enumerate(self.layer_dicts())
+                                              if lc["type"] == "attention" and not lc["mixer"]["v_mix"]))

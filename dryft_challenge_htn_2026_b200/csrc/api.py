@@ -694,8 +694,8 @@ def attention_masked(q, out, gate, out_scale, k_store, v_store, row_pos, row_seq
     _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", q.dtype), _need(v_store, "v_store", q.dtype)
     _need(r1, "r1", torch.float32, 1), _need(r2, "r2", torch.float32, 1), _need(sink, "sink", torch.float32, 1)
-    if head_dim > 256 or v_head_dim > 256 or n_heads % n_kv_heads or (r1 is None) != (r2 is None):
-        raise KernelError(f"attention_masked: head sizes {head_dim}/{v_head_dim} (max 256), heads {n_heads}:{n_kv_heads}")
+    if head_dim > MASKED_MAX_HEAD or v_head_dim > MASKED_MAX_HEAD or n_heads % n_kv_heads or (r1 is None) != (r2 is None):
+        raise KernelError(f"attention_masked: head sizes {head_dim}/{v_head_dim} (max {MASKED_MAX_HEAD}), heads {n_heads}:{n_kv_heads}")
     if q.shape[1] != n_heads * head_dim or out.shape[1] != n_heads * v_head_dim or \
             (gate is not None and gate.shape[1] != n_heads * v_head_dim):
         raise KernelError("attention_masked: q, gate or out of the wrong width")
@@ -716,6 +716,9 @@ def _masked_lib(head_dim, v_head_dim):
     if head_dim % 16 or v_head_dim % 16 or not 16 <= head_dim <= 256 or not 16 <= v_head_dim <= 256:
         raise KernelError(f"bfloat16 masked attention: head sizes {head_dim}/{v_head_dim} not supported (multiples of 16 up to 256)")
     return _lib("attention_masked_bf16.cu", {"HD": head_dim, "HDV": v_head_dim})
+
+
+MASKED_MAX_HEAD = 640      # the float32-arithmetic kernel's largest head (a cached row of latents may be that wide)
 
 
 def masked_bf16_takes(head_dim, v_head_dim):

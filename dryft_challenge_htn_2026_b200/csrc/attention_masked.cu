@@ -32,7 +32,8 @@ __global__ void kv_write_kernel(const T* k, const T* v, long long ld, T* k_store
         v_store[kv_offset(page, nkv, i / hdv, in_page, hdv) + i % hdv] = v[(size_t)t * ld + i];
 }
 
-template <typename T>
+// NR: coordinates of a head that a lane holds (head sizes up to 32 * NR)
+template <typename T, int NR>
 __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long long ldo, const T* gate, long long ldg,
                                         float out_scale, const T* k_store, const T* v_store, const int* row_pos,
                                         const int* row_seq, const int* page_table, int pt_stride, int n_tok, int nh,
@@ -54,9 +55,9 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
     const int kvh = h / (nh / nkv);
     const int* pt = page_table + (size_t)row_seq[t] * pt_stride;
     const T* qr = q + (size_t)t * ldq + (size_t)h * hd;
-    float qv[8], acc[8];
+    float qv[NR], acc[NR];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < NR; i++) {
         const int d = lane + 32 * i;
         qv[i] = d < hd ? to_f(qr[d]) : 0.f;
         acc[i] = 0.f;
@@ -74,7 +75,7 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
         const T* vr = v_store + kv_offset(page, nkv, kvh, j % DK_PAGE, hdv);
         float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < NR; i++) {
             const int d = lane + 32 * i;
             if (d < hd) dot += qv[i] * to_f(kr[d]);
         }
@@ -86,7 +87,7 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
         const float p = expf(s - m_new);
         l = l * alpha + p;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < NR; i++) {
             const int d = lane + 32 * i;
             if (d < hdv) acc[i] = acc[i] * alpha + p * to_f(vr[d]);
         }
@@ -101,7 +102,7 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
     const float inv = alpha / l * out_scale;
     const T* gr = gate ? gate + (size_t)t * ldg + (size_t)h * hdv : nullptr;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
+    for (int i = 0; i < NR; i++) {
         const int d = lane + 32 * i;
         if (d < hdv) {
             float v = acc[i] * inv;
@@ -127,15 +128,19 @@ DK_EXPORT int dk_attention_masked(int dtype, const void* q, long long ldq, void*
                                   int n_tok, int nh, int nkv, int hd, int hdv, int window, int chunk, float scale,
                                   const float* r1, const float* r2, const float* sink, float softcap, int keep_first,
                                   cudaStream_t st) {
-    if (hd > 256 || hdv > 256 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
+    if (hd > 640 || hdv > 640 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)n_tok * nh;
     const unsigned blocks = (unsigned)((warps + 3) / 4);
-    if (dtype == 0)
-        return dk_launch(attention_masked_kernel<float>, dim3(blocks), dim3(128), 0, st, (const float*)q, ldq,
-                         (float*)out, ldo, (const float*)gate, ldg, out_scale, (const float*)k_store,
-                         (const float*)v_store, row_pos, row_seq, page_table, pt_stride, n_tok, nh, nkv, hd, hdv, window,
-                         chunk, scale, r1, r2, sink, softcap, keep_first);
-    return dk_launch(attention_masked_kernel<bf16>, dim3(blocks), dim3(128), 0, st, (const bf16*)q, ldq, (bf16*)out, ldo,
-                     (const bf16*)gate, ldg, out_scale, (const bf16*)k_store, (const bf16*)v_store, row_pos, row_seq,
-                     page_table, pt_stride, n_tok, nh, nkv, hd, hdv, window, chunk, scale, r1, r2, sink, softcap, keep_first);
+    const bool wide = hd > 256 || hdv > 256;       // heads beyond 256 coordinates: 20 a lane instead of 8
+#define AM_LAUNCH(T, NR)                                                                                              \
+    return dk_launch(attention_masked_kernel<T, NR>, dim3(blocks), dim3(128), 0, st, (const T*)q, ldq, (T*)out, ldo,   \
+                     (const T*)gate, ldg, out_scale, (const T*)k_store, (const T*)v_store, row_pos, row_seq, page_table, \
+                     pt_stride, n_tok, nh, nkv, hd, hdv, window, chunk, scale, r1, r2, sink, softcap, keep_first)
+    if (dtype == 0) {
+        if (wide) AM_LAUNCH(float, 20);
+        AM_LAUNCH(float, 8);
+    }
+    if (wide) AM_LAUNCH(bf16, 20);
+    AM_LAUNCH(bf16, 8);
+#undef AM_LAUNCH
 }

@@ -28,8 +28,8 @@ class MaskedAttention(Part):
         s = spec
         if s.num_heads % s.num_kv_heads:
             raise ValueError(f"{s.num_heads} query heads are not a multiple of {s.num_kv_heads} key/value heads")
-        if max(s.head_dim, s.v_head_dim) > 256:
-            raise ValueError(f"attention kernels take head sizes up to 256, not {s.head_dim} / {s.v_head_dim}")
+        if max(s.head_dim, s.v_head_dim) > api.MASKED_MAX_HEAD:
+            raise ValueError(f"attention kernels take head sizes up to {api.MASKED_MAX_HEAD}, not {s.head_dim} / {s.v_head_dim}")
         if s.chunk is not None and s.chunk < 1:
             raise ValueError(f"a chunk of {s.chunk} positions")
         self.n_q, self.n_k = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim

@@ -2,7 +2,7 @@
 
 The model says which names and shapes it wants (``CausalLM.param_decls``); the files say what
 they hold. Every difference — missing, unexpected, wrong shape — is collected and raised as ONE
-``WeightError``. Matrices are cast to the compute dtype (bfloat16 stays bfloat16); parameters a
+``WeightError`` (names a design ships without reading them, ``ModelSpec.unused_tensors``, are let pass). Matrices are cast to the compute dtype (bfloat16 stays bfloat16); parameters a
 part declares ``keep_float32`` (norm weights) are held in float32 whatever the file stores; integer
 tensors would be held as int32. The reference loads every ``*.safetensors`` of the folder into one
 dict and pops names from it (engine/engine.py:282-309), raising a bare KeyError on a missing name
@@ -66,7 +66,7 @@ def load_weights(model, folder):
         tied = spec.tie_embeddings if spec.tie_embeddings is not None else spec.head_name not in have
     decls = model.param_decls(tied)
     missing = [n for n in decls if n not in have]
-    unexpected = [n for n in have if n not in decls]
+    unexpected = [n for n in have if n not in decls and n not in spec.unused_tensors]
     wrong = [(n, have[n][1], decls[n].shape) for n in decls if n in have and tuple(have[n][1]) != tuple(decls[n].shape)]
     if missing or unexpected or wrong:
         raise WeightError(folder, missing, unexpected, wrong)

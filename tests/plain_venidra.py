@@ -68,12 +68,15 @@ def attention(h, w, pre, m, eps, v_first):
     """Grouped heads, rotation of the first rot.dims coordinates by halves, unit RMS of q and k after it, chunk mask,
     values blended with the first blending layer's. Returns (output, this layer's values before blending)."""
     T = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, D = m["heads"], m["dim"]
+    G, Dv = m.get("kv_heads", H), m.get("vdim", D)
     q = (h @ w[pre + "q"].T).view(T, H, D)
     k = (h @ w[pre + "k"].T).view(T, G, D)
     v = (h @ w[pre + "v"].T).view(T, G, Dv)
-    a = angles(T, m["rot"]["dims"], m["rot"]["base"])
-    q, k = rms(rotate_halves(q, a), eps), rms(rotate_halves(k, a), eps)
+    if m.get("rot") and m["rot"]["dims"]:
+        a = angles(T, m["rot"]["dims"], m["rot"]["base"])
+        q, k = rotate_halves(q, a), rotate_halves(k, a)
+    q, k = rms(q, eps), rms(k, eps)
     v_own = v
     if m.get("v_mix") and v_first is not None:
         lam = w[pre + "vmix"]
@@ -81,7 +84,7 @@ def attention(h, w, pre, m, eps, v_first):
     rep = H // G
     ke, ve = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
     score = torch.einsum("ihd,jhd->hij", q, ke) * m["scale"]
-    o = softmax_heads(score, chunk_mask(T, m["mask"]["size"]), ve)
+    o = softmax_heads(score, chunk_mask(T, m["mask"]["size"] if m.get("mask") else T), ve)
     return o @ w[pre + "o"].T, v_own
 
 
@@ -93,13 +96,13 @@ def latent_attention(h, w, pre, m, eps):
     q = (cq @ w[pre + "uq"].T).view(T, H, D + R)
     kv = h @ w[pre + "dkv"].T
     c = rms(kv[:, :L], eps) * w[pre + "dkv.norm"]
-    a = angles(T, R, m["rot"]["base"])
+    a = angles(T, m["rot"].get("dims", R), m["rot"]["base"])
     k_rot = rotate_pairs(kv[:, None, L:], a)                       # [T, 1, R]
     q_rot = rotate_pairs(q[..., D:], a)
     k_plain = (c @ w[pre + "uk"].T).view(T, H, D)
     v = (c @ w[pre + "uv"].T).view(T, H, Dv)
     score = (torch.einsum("ihd,jhd->hij", q[..., :D], k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot[:, 0])) * m["scale"]
-    o = softmax_heads(score, window_mask(T, m["mask"]["size"]), v)
+    o = softmax_heads(score, window_mask(T, m["mask"]["size"] if m.get("mask") else T), v)
     return o @ w[pre + "o"].T
 
 
@@ -110,7 +113,7 @@ def feed_forward(h, w, pre):
 def forward(cfg, w, tokens, layers_out=None):
     """Logits [T, vocab] of one whole sequence. ``layers_out``: a list that receives the stream after every layer."""
     eps = cfg["norm"]["eps"]
-    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     v_first = None
     for i, lc in enumerate(cfg["layers"]):
         pre = f"l{i}."
@@ -135,3 +138,26 @@ def forward(cfg, w, tokens, layers_out=None):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits
+
+
+def read_model(folder):
+    """(config dict, name -> float64 tensor) of a model folder."""
+    import json
+    import os
+
+    from safetensors import safe_open
+
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    w = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            w[k] = f.get_tensor(k).to(F)
+    return cfg, w
+
+
+def masked_softmax_attention(q, k, v, mask, scale):
+    """q [T, H, D], k [T, G, D], v [T, G, Dv], mask [T, T] -> [T, H * Dv], heads grouped onto the G key/value heads."""
+    rep = q.shape[1] // k.shape[1]
+    score = torch.einsum("ihd,jhd->hij", q, k.repeat_interleave(rep, 1)) * scale
+    return softmax_heads(score, mask, v.repeat_interleave(rep, 1))
