@@ -649,10 +649,153 @@ def pibulix_kernel_times(torch, dk, pk, width, heads, kv_heads, ff_qwen, window)
 
 
 PIBULIX_WINDOW = 1024
+VENIDRA_WINDOW = 1024
+VENIDRA_CHUNK = 2048
+
+
+def venidra_config(width, heads, kv_heads, ff_qwen, layers, vocab):
+    """A Venidra model of Qwen3's width, head counts, head size 128, layer count and feed-forward size: attention layers
+    (half the head rotated, unit RMS of q and k, chunks of 2,048, values blended with the first layer's) in turn with
+    layers of attention through latents (a query latent of 0.3 of the width, a key/value latent of 512 and a shared rotated
+    key part of 64, as published models of that kind have them, plain key and value heads of 128, a window of 1,024)."""
+    hd = 128
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "v_mix": True,
+                     "rot": {"dims": hd // 2, "base": 1e6}, "mask": {"size": VENIDRA_CHUNK}},
+           "mlp": {"kind": "dense", "ff": ff_qwen}}
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": hd, "rot_dim": 64, "vdim": hd, "q_rank": width * 3 // 10 // 64 * 64, "kv_rank": 512,
+                     "scale": (hd + 64) ** -0.5, "rot": {"base": 1e4, "dims": 64}, "mask": {"size": VENIDRA_WINDOW}},
+           "mlp": {"kind": "dense", "ff": ff_qwen}}
+    return dict(architecture="Venidra", vocab=vocab, width=width, norm={"eps": 1e-6}, embedding={"scale": 1.0}, logit_scale=1.0,
+                logit_softcap=30.0, layers=[att if i % 2 == 0 else lat for i in range(layers)])
+
+
+def venidra_kernel_times(torch, dk, pk, cfg_d, heads, kv_heads):
+    """The design's own mixer steps alone (the parts of a model of ``cfg_d``, so each step runs whichever kernel the part
+    picks), beside Qwen3's attention kernels at the same head counts: CUDA events around one step, L2 flushed before
+    each (a 256 MB write), median of 5 after 2 untimed."""
+    from dryft_challenge_htn_2026_b200.cache import Cache, KVRequest
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.engine.batch import build_context
+    from dryft_challenge_htn_2026_b200.parts import Runtime, build_part
+    from dryft_challenge_htn_2026_b200.parts.attention import QueryTiles
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    hd = 128
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for i in range(7):
+            flush.fill_(float(i))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[2:]) * 1e3        # microseconds
+
+    def flops_rec(us, flops):
+        return {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}
+
+    def bytes_rec(us, moved):
+        return {"us": round(us, 1), "gbs": round(moved / us / 1e3, 1), "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+
+    spec = dk.config_from_dict(cfg_d).to_spec()
+    rt = Runtime(dev, bf)
+    g = torch.Generator(device=dev).manual_seed(1)
+    att, lat = build_part(spec.layers[0].mixer, rt), build_part(spec.layers[1].mixer, rt)
+    for part in (att, lat):
+        part.bind({d.name: (torch.rand(d.shape, generator=g, device=dev) * 0.5 if d.init == "fraction" else
+                            torch.randn(d.shape, generator=g, device=dev) * 0.02 + (1.0 if d.init == "norm" else 0.0)).to(
+            torch.float32 if d.keep_float32 else bf) for d in part.param_decls()})
+        part.prepare(16384)
+    ls = lat.spec
+    H, L, R, D, Dv, Qr = ls.num_heads, ls.kv_rank, ls.rot_dim, ls.head_dim, ls.v_head_dim, ls.q_rank
+    chunk, window = att.spec.chunk, ls.window
+    out = {}
+
+    def fill(cache, n):
+        for e in range(n):
+            v = cache.views(e)[0]
+            v.k.normal_(), v.v.normal_()
+
+    def steps(ctx, cache, rows, tag, keys_att, keys_lat, pairs_att, pairs_lat, pairs_full):
+        """One record per step of the two mixers; ``pairs_*``: (query, key) pairs in sight, ``keys_*``: keys a row reads."""
+        a_views, l_views, f = cache.views(0), cache.views(1), cache.views(2)[0]
+        proj = torch.randn(rows, att.n_in, device=dev).to(bf)
+        ctx.carry = {("value_mix", att.n_v): torch.randn(rows, att.n_v, device=dev).to(bf)}
+        mid = torch.empty(rows, att.n_mid, dtype=bf, device=dev)
+        prepared = att.prepared_rows(ctx, a_views, proj)
+        us = timed(lambda: att.prepared_rows(ctx, a_views, proj))
+        out[f"rotation_unit_rms_blend_cache_write_{tag}"] = bytes_rec(us, rows * (2 * att.n_qkv + att.n_k + 2 * att.n_v) * 2)
+        q, k, v = prepared[:, :att.n_q], prepared[:, att.n_q:att.n_q + att.n_k], prepared[:, att.n_q + att.n_k:]
+        us = timed(lambda: att.attend(ctx, a_views[0], q, k, v, None, mid, 1.0, writes=False))
+        out[f"chunk_attention_{tag}"] = flops_rec(us, 4 * heads * hd * pairs_att) if pairs_att else \
+            dict(bytes_rec(us, rows * kv_heads * keys_att * 2 * hd * 2), keys=keys_att)
+        down = torch.randn(rows, lat.n_down, device=dev).to(bf)
+        cq = torch.empty(rows, Qr, dtype=bf, device=dev)
+        cos, sin, rot = lat._tables(ctx)
+        table = ctx.tables[l_views[0].group]
+        us = timed(lambda: api.latent_norm_rope_write(down, cq, lat.q_norm_w, lat.kv_norm_w, ls.norm_eps, cos, sin, rot, ctx.row_pos,
+                                                      ctx.row_seq, Qr, L, R, l_views[0].k, l_views[0].v, table))
+        out[f"latent_norms_rotation_cache_write_{tag}"] = bytes_rec(us, rows * (lat.n_down + Qr + 2 * L + R) * 2)
+        qu = torch.randn(rows, lat.n_q, device=dev).to(bf)
+        ql = lat.queries(ctx, qu)
+        us = timed(lambda: lat.queries(ctx, qu))
+        out[f"latent_query_heads_{tag}"] = flops_rec(us, 2 * rows * H * D * L) if pairs_lat else \
+            bytes_rec(us, H * D * L * 2 + rows * (lat.n_q + H * lat.lat) * 2)
+        o_lat = torch.empty(rows, H * L, dtype=bf, device=dev)
+        us = timed(lambda: lat.core.attend(ctx, l_views[0], ql, None, None, None, o_lat, 1.0, writes=False))
+        out[f"latent_attention_{tag}"] = flops_rec(us, 2 * H * (lat.lat + L) * pairs_lat) if pairs_lat else \
+            dict(bytes_rec(us, rows * keys_lat * lat.lat * 2), keys=keys_lat)
+        us = timed(lambda: lat.values(o_lat))
+        out[f"latent_value_heads_{tag}"] = flops_rec(us, 2 * rows * H * Dv * L) if pairs_lat else \
+            bytes_rec(us, H * Dv * L * 2 + rows * (H * L + lat.n_mid) * 2)
+        return f
+
+    for tokens in (2048, 8192):
+        plans = att.step_plans() + lat.step_plans() + [QueryTiles(api.TC_TILE_ROWS)]
+        cache = Cache([att.cache_requests(), lat.cache_requests(), [KVRequest(kv_heads, hd, None, bf)]], tokens + 64, 2, dev)
+        slot = cache.begin()
+        ctx = build_context(cache, [(slot, [0] * tokens, [])], dev, plans=plans)
+        fill(cache, 3)
+        pairs_att = sum(i % chunk + 1 for i in range(tokens))
+        pairs_lat = sum(min(i + 1, window) for i in range(tokens))
+        full = tokens * (tokens + 1) // 2
+        f = steps(ctx, cache, tokens, str(tokens), None, None, pairs_att, pairs_lat, full)
+        q = torch.randn(tokens, heads * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        us = timed(lambda: api.attention_prefill_tc(q, o, f.k, f.v, ctx.plans[plans[-1].key], ctx.cu_q, ctx.seq_pos0, ctx.tables[f.group],
+                                                    heads, kv_heads, hd, None, hd ** -0.5))
+        out[f"qwen3_attention_prefill_{tokens}"] = flops_rec(us, 4 * heads * hd * full)
+        cache.end(slot)
+        del cache, q, o
+    for batch in (8, 64):
+        context = 3000       # 952 keys of the newest chunk and the window's 1,024 in sight
+        cache = Cache([att.cache_requests(), lat.cache_requests(), [KVRequest(kv_heads, hd, None, bf)]], batch * (context + 64), batch, dev)
+        slots = [cache.begin() for _ in range(batch)]
+        for sl in slots:
+            cache.reserve(sl, context + 1)
+            cache.length[sl] = context
+        ctx = build_context(cache, [(sl, [0], []) for sl in slots], dev, plans=att.step_plans() + lat.step_plans())
+        fill(cache, 3)
+        f = steps(ctx, cache, batch, f"decode_b{batch}", context % chunk + 1, min(window, context + 1), 0, 0, 0)
+        q = torch.randn(batch, heads * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        nsplit = api.decode_splits(batch, kv_heads, heads // kv_heads, ctx.tables[f.group].shape[1])
+        ws = api.attention_decode_ws(batch, heads, hd, nsplit, dev)
+        us = timed(lambda: api.attention_decode_bf16(q, o, f.k, f.v, ctx.row_pos, ctx.tables[f.group], heads, kv_heads, hd, None,
+                                                     hd ** -0.5, nsplit, *ws))
+        out[f"qwen3_attention_decode_b{batch}"] = dict(bytes_rec(us, batch * kv_heads * (context + 1) * 2 * hd * 2), keys=context + 1)
+        del cache, q, o
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_design(args):
-    """``--design nilivik`` / ``--design pibulix``: prefill and decode of that decoder at Qwen3 layer sizes (random weights,
+    """``--design nilivik`` / ``--design pibulix`` / ``--design venidra``: prefill and decode of that decoder at Qwen3 layer sizes (random weights,
     ``--layers`` layers, default 4) beside Qwen3 itself at the same width, layer count and parameters a
     layer, and the design's mixer kernels alone beside Qwen3's attention kernels. One JSON line."""
     import torch
@@ -669,7 +812,11 @@ def run_design(args):
            "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
     for size in args.design_sizes.split(","):
         q = dict(SIZES[size]["config"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True)
-        if args.design == "pibulix":
+        if args.design == "venidra":
+            n = venidra_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers, vocab)
+            rec = {"width": q["hidden_size"], "chunk": VENIDRA_CHUNK, "window": VENIDRA_WINDOW, "q_rank": n["layers"][1]["mixer"]["q_rank"],
+                   "kv_rank": 512, "rot_dim": 64}
+        elif args.design == "pibulix":
             n = pibulix_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers,
                                vocab, PIBULIX_WINDOW)
             rec = {"width": q["hidden_size"], "window": PIBULIX_WINDOW, "expert_ff": n["layers"][1]["mlp"]["expert"]["ff"]}
@@ -691,7 +838,9 @@ def run_design(args):
             rec[name] = r
             del model
             torch.cuda.empty_cache()
-        if args.design == "pibulix":
+        if args.design == "venidra":
+            rec["kernels"] = venidra_kernel_times(torch, dk, pk, n, q["num_attention_heads"], q["num_key_value_heads"])
+        elif args.design == "pibulix":
             rec["kernels"] = pibulix_kernel_times(torch, dk, pk, q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"],
                                                   q["intermediate_size"], PIBULIX_WINDOW)
         else:
@@ -902,7 +1051,7 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --prefill-only: a prompt of another length")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
-    ap.add_argument("--design", default=None, choices=["nilivik", "pibulix"],
+    ap.add_argument("--design", default=None, choices=["nilivik", "pibulix", "venidra"],
                     help="instead of the default workload: prefill and decode of this design at Qwen3 layer sizes beside Qwen3 "
                          "itself at equal size, and its mixer kernels alone (one JSON line of its own)")
     ap.add_argument("--design-sizes", default="4b,8b", help="with --design: which of the layer sizes")

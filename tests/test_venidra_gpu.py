@@ -202,7 +202,7 @@ def test_unit_rms_comes_after_the_rotation_not_before():
     """With a part of the head rotated the two orders agree (a rotation keeps the length); the test pins the epsilon's
     place and that no weight is applied: tiny heads, where eps decides the result."""
     T, H, D = 3, 2, 8
-    q = (rnd(T, H, D, seed=1) * 1e-3).float()
+    q = (rnd(T, H, D, seed=1) * 1e-4).float()
     proj = torch.cat([q.reshape(T, -1), q.reshape(T, -1)[:, :D], q.reshape(T, -1)[:, :D]], 1).to(DEV)
     out = torch.empty_like(proj)
     cos, sin = build_part(RotaryPartSpec(4, 100.0), Runtime(DEV, torch.float32)).tables(8)
@@ -213,7 +213,7 @@ def test_unit_rms_comes_after_the_rotation_not_before():
     a = torch.stack([plain.angles(1, 4, 100.0, pos0=p)[0] for p in (0, 3, 7)])
     ref = plain.rms(plain.rotate_halves(q.double(), a), 1e-5).reshape(T, -1)
     assert float((out[:, :H * D].cpu().double() - ref).abs().max()) < 1e-6
-    assert float(ref.abs().max()) < 0.5          # eps dominates: without it the entries would be of order 1
+    assert float(ref.abs().max()) < 0.2          # eps dominates: without it the entries would be of order 1
 
 
 def attention_case(dtype, H, G, D, V, chunk, window, lens_steps, plant=None, seed=0):
