@@ -103,7 +103,9 @@ class MaskedAttentionSpec:
     (a ``RotaryPartSpec``); the norm comes before the rotation unless ``norm_after_rotation``.
     ``value_mix``: the layers of a model that say it share the values of the first of them ("source": it leaves its
     values of the step's tokens for the others and caches them as they are); every other ("blend") caches and uses
-    v <- (1 - lam) v + lam v_source with its learned number ``vmix`` (both kinds hold the tensor; the source's is unused)."""
+    v <- (1 - lam) v + lam v_source with its learned number ``vmix`` (both kinds hold the tensor; the source's is unused).
+    ``values_in_keys``: whoever fills the cache makes a value row the first ``v_head_dim`` numbers of its key row (the rows of
+    latents of an attention through latents), so a kernel may read the key rows alone."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -123,6 +125,7 @@ class MaskedAttentionSpec:
     position: Optional[Any] = None
     norm_after_rotation: bool = False
     value_mix: Optional[str] = None
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

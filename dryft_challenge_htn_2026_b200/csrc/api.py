@@ -745,6 +745,62 @@ def attention_masked_prefill_bf16(q, out, gate, out_scale, k_store, v_store, til
            "attention_masked_prefill_bf16")
 
 
+SHARED_ROWS_MAX_SPLITS = 16
+
+
+def shared_rows_takes(head_dim, v_head_dim):
+    """Whether the kernel for cached rows that are key and value at once is built for these sizes."""
+    return head_dim % 16 == 0 and v_head_dim % 32 == 0 and 32 <= v_head_dim <= min(512, head_dim) and head_dim <= 640
+
+
+def shared_rows_tile_queries(group):
+    """Queries of a prompt that one block of ``attention_shared_rows_bf16`` takes: 64 rows = queries x heads of a group."""
+    return max(1, 64 // min(group, 64))
+
+
+def shared_rows_operands(q, out):
+    return q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+
+
+def shared_rows_splits(rows, n_heads, n_kv_heads, table_pages, window, chunk):
+    """Blocks that share a single token's keys: enough to give every SM one, at least two half pages each."""
+    most = min([x for x in (chunk, window, table_pages * PAGE) if x])
+    blocks = rows * n_kv_heads * -(-(n_heads // n_kv_heads) // 64)
+    return max(1, min(SHARED_ROWS_MAX_SPLITS, sm_count() // blocks, (most // 32 + 2) // 2))
+
+
+def shared_rows_ws(rows, n_heads, v_head_dim, nsplit, device):
+    return (torch.empty(rows * n_heads * nsplit * v_head_dim, dtype=torch.float32, device=device),
+            torch.empty(rows * n_heads * nsplit * 2, dtype=torch.float32, device=device))
+
+
+def attention_shared_rows_bf16(q, out, out_scale, k_store, page_table, n_heads, n_kv_heads, head_dim, v_head_dim, window, chunk,
+                               scale, tiles=None, cu_q=None, seq_pos0=None, row_pos=None, nsplit=1, ws=None):
+    """Masked softmax attention (bfloat16, mma.sync) whose values are the first ``v_head_dim`` numbers of the cached key
+    rows, all query heads of a group in one block. Prompts: ``tiles`` [n, 2] = (sequence, first query of a tile of
+    ``shared_rows_tile_queries`` queries), ``cu_q``, ``seq_pos0``. Single tokens: ``row_pos`` [rows] (negative: padding),
+    page table row i for row i, the keys of a row in ``nsplit`` runs with ``ws`` = ``shared_rows_ws`` when nsplit > 1."""
+    _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", torch.bfloat16)
+    if not shared_rows_takes(head_dim, v_head_dim) or n_heads % n_kv_heads or not shared_rows_operands(q, out):
+        raise KernelError(f"attention_shared_rows_bf16: sizes {head_dim}/{v_head_dim}, head counts or row strides not supported")
+    if tiles is not None:
+        _need(tiles, "tiles", torch.int32, 2), _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1)
+        n_items, nsplit = tiles.shape[0], 1
+    else:
+        _need(row_pos, "row_pos", torch.int32, 1)
+        n_items = row_pos.shape[0]
+        if q.shape[0] != n_items or (nsplit > 1 and (ws is None or ws[0].numel() < n_items * n_heads * nsplit * v_head_dim)):
+            raise KernelError("attention_shared_rows_bf16: one query row per position, and scratch for the parts of a split")
+    lib = _lib("attention_shared_rows.cu", {"HD": head_dim, "HDV": v_head_dim})
+    _check(lib, lib.dk_attn_shared_rows_bf16(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), c_float(out_scale),
+                                             _p(k_store), _p(tiles), n_items, _p(cu_q), _p(seq_pos0), _p(row_pos), _p(page_table),
+                                             page_table.shape[1], n_heads, n_kv_heads, int(window or 0), int(chunk or 0),
+                                             c_float(scale), nsplit, _p(ws[0]) if nsplit > 1 else None,
+                                             _p(ws[1]) if nsplit > 1 else None, _stream()),
+           "attention_shared_rows_bf16", kernels=2 if nsplit > 1 else 1)
+
+
 def masked_tc_takes(q, out, gate, head_dim, v_head_dim):
     """Whether the tcgen05 prefill attention in its masked build takes these operands: equal head sizes of
     64 or 128, rows a multiple of 8 elements apart and on 16-byte boundaries."""

@@ -125,7 +125,8 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
     jobs = [("elementwise.cu", None), ("attention_generic.cu", None), ("gemm.cu", None), ("gemv_stream.cu", None),
             ("gemm_tc.cu", None), ("sampling.cu", None),
             ("sample_noalloc.cu", None), ("attention_masked.cu", None), ("linear_attention.cu", None),
-            ("short_conv.cu", None), ("moe.cu", None), ("moe_tiles.cu", None)]
+            ("short_conv.cu", None), ("moe.cu", None), ("moe_tiles.cu", None), ("latent.cu", None),
+            ("attention_shared_rows.cu", {"HD": 576, "HDV": 512})]
     jobs += [("attention_bf16.cu", {"HD": hd}) for hd in head_dims]
     jobs += [("attention_tc.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]
     jobs += [("attention_tc.cu", {"HD": hd, "DK_MASKED": 1}) for hd in head_dims if hd in (64, 128)]

@@ -64,12 +64,17 @@ class MaskedAttention(Part):
         # kernel and of the split single-token kernel (equal head sizes); the mma.sync kernels for other sizes lack them
         self.plain_options = s.softcap is None and not s.keep_first
         self.tiles = QueryTiles(api.MASKED_TILE_ROWS) if self.tensor_core else None
+        # value rows that are the key rows' first numbers, of sizes beyond those kernels: all heads of a group in one
+        # block over the key rows alone (prompts and single tokens)
+        self.shared_rows = rt.dtype == torch.bfloat16 and not self.tensor_core and s.values_in_keys and self.plain_options \
+            and not (s.distance_bias or s.sink or s.unit_sink or s.output_gate) and api.shared_rows_takes(s.head_dim, s.v_head_dim)
+        self.row_tiles = QueryTiles(api.shared_rows_tile_queries(s.num_heads // s.num_kv_heads)) if self.shared_rows else None
         # equal head sizes of 64 or 128: prompts run on the tcgen05 kernel (its masked build), in tiles of 128 queries
         self.tc_tiles = QueryTiles(api.TC_TILE_ROWS) if self.tensor_core and s.head_dim == s.v_head_dim \
             and s.head_dim in api.TC_ATTENTION_HEAD_DIMS else None
 
     def step_plans(self):
-        return [t for t in (self.tiles, self.tc_tiles) if t is not None]
+        return [t for t in (self.tiles, self.tc_tiles, self.row_tiles) if t is not None]
 
     def param_decls(self):
         s = self.spec
@@ -202,6 +207,15 @@ class MaskedAttention(Part):
                                                     self.r1, self.r2, self.sink, k if writes else None, v if writes else None, ws)
         if writes:
             api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
+        if self.shared_rows and gate is None and api.shared_rows_operands(q, mid):
+            if not ctx.is_decode:
+                return api.attention_shared_rows_bf16(q, mid, scale, kv.k, table, *sizes, tiles=ctx.plans[self.row_tiles.key],
+                                                      cu_q=ctx.cu_q, seq_pos0=ctx.seq_pos0)
+            nsplit = api.shared_rows_splits(ctx.n_tok, s.num_heads, s.num_kv_heads, table.shape[1], s.window, s.chunk)
+            ws = ctx.scratch(("shared_rows", ctx.n_tok, s.num_heads, s.v_head_dim, nsplit),
+                             lambda: api.shared_rows_ws(ctx.n_tok, s.num_heads, s.v_head_dim, nsplit, self.rt.device)) \
+                if nsplit > 1 else None
+            return api.attention_shared_rows_bf16(q, mid, scale, kv.k, table, *sizes, row_pos=ctx.row_pos, nsplit=nsplit, ws=ws)
         if self.tc_tiles is not None and not ctx.is_decode and api.masked_tc_takes(q, mid, gate, s.head_dim, s.v_head_dim):
             return api.attention_masked_prefill_tc(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tc_tiles.key], ctx.cu_q,
                                                    ctx.seq_pos0, table, s.num_heads, s.num_kv_heads, s.head_dim, s.window,

@@ -5,7 +5,8 @@ forward = one fused down projection [dq; dkv] -> (norm of the query latent; norm
 rotation of the shared key part, both straight into the cache; one kernel) -> query up projection -> per head the
 plain key's up projection moved to the query's side, q_h <- [W_uk_h^T q_plain | q_rot rotated], so that a score is
 q_h . [c | k_rot] against the cached row itself -> attention with all heads on the one cached head (the masked
-attention's kernels: float32-arithmetic, mma.sync prompts, single tokens), whose values are the latents -> per head
+attention's kernels: float32-arithmetic, mma.sync prompts, single tokens; rows wider than 256 on the kernel for rows that
+are key and value at once), whose values are the latents -> per head
 W_uv times the latent output -> output projection. Nothing per head is ever cached or recomputed for old tokens, so
 a step costs the same however a prompt is cut.
 """
@@ -19,8 +20,9 @@ from .base import ParamDecl, Part, build_part, register_part
 from .linear import linear
 
 # steps of more rows than this take the per-head products of a bfloat16 model through the library's batched matrix
-# product (tensor cores); up to it, and in float32, the row kernels
-HEAD_PRODUCT_ROWS = 32
+# product (tensor cores); float32 takes the row kernels. (At 32 heads of 128 over latents of 512 the row kernels took
+# 127 and 57 us for 8 tokens, the batched product 10.)
+HEAD_PRODUCT_ROWS = 0
 
 
 class LatentAttention(Part):
@@ -39,7 +41,7 @@ class LatentAttention(Part):
         # the attention itself: every query head on the one cached head, keys [c | k_rot], values c
         self.core = MaskedAttention(MaskedAttentionSpec(
             hidden_size=s.hidden_size, num_heads=s.num_heads, num_kv_heads=1, head_dim=self.lat, v_head_dim=s.kv_rank,
-            scale=s.scale, chunk=s.chunk, window=s.window), rt)
+            scale=s.scale, chunk=s.chunk, window=s.window, values_in_keys=True), rt)
         self.max_positions = 0
 
     def param_decls(self):

@@ -216,24 +216,29 @@ def test_unit_rms_comes_after_the_rotation_not_before():
     assert float(ref.abs().max()) < 0.2          # eps dominates: without it the entries would be of order 1
 
 
-def attention_case(dtype, H, G, D, V, chunk, window, lens_steps, plant=None, seed=0):
+def attention_case(dtype, H, G, D, V, chunk, window, lens_steps, plant=None, seed=0, values_in_keys=False):
     """The attention part's ``mix`` with nothing between projection and cache (cache write and whichever attention kernel
     the part picks) over one sequence cut into steps, a second sequence beside it, against the plain softmax over the
     whole sequence. ``plant`` = (query position, key position, strength): that key is given the query's direction, so
-    that its score stands out, and a value of 5."""
+    that its score stands out, and a value of 5. ``values_in_keys``: every value row is the start of its key row (what an
+    attention through latents caches), which the part may use to read the key rows alone."""
     T = sum(lens_steps)
     q, k, v = rnd(T, H, D, seed=seed), rnd(T, G, D, seed=seed + 1), rnd(T, G, V, seed=seed + 2)
     if plant:
         qi, kj, strength = plant
         k[kj] = strength * q[qi, 0] / q[qi, 0].norm()
         v[kj] = 5.0
+    if values_in_keys:
+        v = k[..., :V].clone()
     q, k, v = (x.to(dtype).double() for x in (q, k, v))
     scale = 0.9 * D ** -0.5
     mask = plain.chunk_mask(T, chunk or T) & plain.window_mask(T, window or T)
     ref = plain.masked_softmax_attention(q, k, v, mask, scale)
     spec = MaskedAttentionSpec(hidden_size=8, num_heads=H, num_kv_heads=G, head_dim=D, v_head_dim=V, scale=scale, chunk=chunk,
-                               window=window)
+                               window=window, values_in_keys=values_in_keys)
     part = build_part(spec, Runtime(DEV, dtype))
+    if values_in_keys and dtype == torch.bfloat16 and max(D, V) > 256:
+        assert part.shared_rows        # the kernel under test is the one that runs
     cache = Cache([part.cache_requests()], 64 * 40, 4, DEV)
     other, slot = cache.begin(), cache.begin()
     t0, got = 0, []
@@ -262,6 +267,36 @@ def attention_case(dtype, H, G, D, V, chunk, window, lens_steps, plant=None, see
 def test_attention_under_a_chunk_mask_or_a_window(dtype, H, G, D, V, chunk, window):
     got, ref = attention_case(dtype, H, G, D, V, chunk, window, [131, 2, 1, 1, 40, 1, 1, 1, 90])
     close(got, ref, dtype, "attention")
+
+
+# value rows that are the start of the key rows, wider than 256: groups of 3 (21 queries a block), of 70 (two blocks of heads
+# a query), of 1 (64 queries a block) and of 32; a chunk, windows smaller and larger than a page, no mask (single tokens' keys
+# dealt out to several blocks)
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,D,V,chunk,window", [(6, 2, 320, 288, None, 33), (70, 1, 272, 32, 50, None), (3, 3, 288, 288, None, None),
+                                                  (32, 1, 576, 512, None, 100)])
+def test_attention_over_rows_that_are_key_and_value(dtype, H, G, D, V, chunk, window):
+    got, ref = attention_case(dtype, H, G, D, V, chunk, window, [131, 2, 1, 1, 40, 1, 1, 1, 90], values_in_keys=True)
+    close(got, ref, dtype, "attention over shared rows")
+
+
+@pytest.mark.parametrize("where", ["prompt", "decoded"])
+@pytest.mark.parametrize("edge", ["first of the chunk", "last of the chunk before", "last inside the window", "first outside the window",
+                                  "far key among hundreds", "page border", "half page border"])
+def test_a_planted_row_shows_inside_and_is_hidden_outside(where, edge):
+    """The same edges on the kernel for rows that are key and value at once (bfloat16, rows of 288 with values of 256): the
+    head's output is the planted row's start when it is seen."""
+    qi, D, V = 300, 288, 256
+    chunk, window, kj, seen = {"first of the chunk": (70, None, 280, True), "last of the chunk before": (70, None, 279, False),
+                               "last inside the window": (None, 70, 231, True), "first outside the window": (None, 70, 230, False),
+                               "far key among hundreds": (None, None, 1, True), "page border": (None, 70, 256, True),
+                               "half page border": (None, 13, 288, True)}[edge]
+    lens = [qi + 20] if where == "prompt" else [qi - 10] + [1] * 30
+    got, ref = attention_case(torch.bfloat16, 4, 1, D, V, chunk, window, lens, plant=(qi, kj, 25.0), seed=3, values_in_keys=True)
+    close(got, ref, torch.bfloat16, edge)
+    planted = 25.0 * rnd(sum(lens), 4, D, seed=3)[qi, 0] / rnd(sum(lens), 4, D, seed=3)[qi, 0].norm()
+    off = float((got[qi, :V] - planted[:V].to(torch.bfloat16).double()).abs().max())
+    assert (off < 0.5) == seen, (edge, off)
 
 
 @pytest.mark.parametrize("dtype,D,V", [(torch.float32, 32, 32), (torch.bfloat16, 32, 16), (torch.bfloat16, 64, 64), (torch.bfloat16, 80, 64)])
@@ -323,11 +358,13 @@ def latent_case(dtype, H, D, R, V, q_rank, kv_rank, window, lens_steps, base=100
 
 
 # latents wider and narrower than the heads, a rotated part as wide as the plain one and wider, one head, sizes no
-# tensor-core kernel takes (24 + 6), a cached row of 128 and one of 320, windows of 1, 7, 64, 200 and none
+# tensor-core kernel takes (24 + 6), a cached row of 128 and ones of 320 and 336 (5 and 66 heads on them), windows of 1, 7, 64,
+# 200 and none
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,D,R,V,q_rank,kv_rank,window", [(4, 16, 16, 32, 24, 32, 40), (2, 32, 8, 16, 16, 48, 7), (3, 12, 6, 20, 10, 24, 33),
                                                            (2, 64, 16, 48, 40, 112, 200), (3, 16, 32, 16, 64, 16, 1), (1, 48, 32, 80, 8, 96, None),
-                                                           (8, 32, 16, 80, 96, 64, 64), (2, 24, 64, 40, 32, 256, 50)])
+                                                           (8, 32, 16, 80, 96, 64, 64), (2, 24, 64, 40, 32, 256, 50),
+                                                           (5, 16, 32, 24, 16, 288, 50), (66, 8, 16, 8, 12, 320, None)])
 def test_latent_attention_in_prompts_portions_and_single_tokens(dtype, H, D, R, V, q_rank, kv_rank, window):
     got, ref = latent_case(dtype, H, D, R, V, q_rank, kv_rank, window, [70, 2, 1, 1, 33, 1, 1, 1, 60, 1])
     close(got, ref, dtype, "latent attention", slack=1.0)
