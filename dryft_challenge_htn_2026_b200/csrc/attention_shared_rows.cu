@@ -7,7 +7,7 @@
 //
 // A block of 8 warps owns 64 rows of the (query, head of the group) plane of one sequence and one key/value head:
 // with G heads in a group, 64 / G consecutive queries with all their heads (G >= 64: one query and 64 of its heads).
-// It keeps its 64 query rows in shared memory and walks the keys in half pages of 32, staged by cp.async two deep:
+// It keeps its 64 query rows in shared memory and walks the keys in half pages of 32, staged by cp.async three deep:
 //   scores : warp (r, c) takes rows 16 r .. 16 r + 15 against keys 16 c .. 16 c + 15 of the half page, query and key
 //            fragments by ldmatrix, mma.sync m16n8k16; the two warps of a row block meet their row maxima in shared
 //            memory and leave P there;
@@ -31,7 +31,8 @@ constexpr int SR_PSTR = SR_KEYS + 8;
 constexpr int SR_Q_ELEMS = SR_ROWS * SR_STR;
 constexpr int SR_K_ELEMS = SR_KEYS * SR_STR;
 constexpr int SR_P_ELEMS = SR_ROWS * SR_PSTR;
-constexpr size_t SR_SMEM_BYTES = (size_t)(SR_Q_ELEMS + 2 * SR_K_ELEMS + SR_P_ELEMS) * sizeof(bf16) + 4 * SR_ROWS * sizeof(float);
+constexpr int SR_STAGES = 3;
+constexpr size_t SR_SMEM_BYTES = (size_t)(SR_Q_ELEMS + SR_STAGES * SR_K_ELEMS + SR_P_ELEMS) * sizeof(bf16) + 4 * SR_ROWS * sizeof(float);
 constexpr int SR_HALF = HDV / 2;            // value columns a warp holds
 
 __device__ __forceinline__ void sr_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -90,7 +91,7 @@ attn_shared_rows_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, 
     extern __shared__ __align__(16) bf16 smem[];
     bf16* Qs = smem;
     bf16* Ks = Qs + SR_Q_ELEMS;
-    bf16* Ps = Ks + 2 * SR_K_ELEMS;
+    bf16* Ps = Ks + SR_STAGES * SR_K_ELEMS;
     float* smax = reinterpret_cast<float*>(Ps + SR_P_ELEMS);      // [2][64]: a row's maximum over each half of the turn's keys
     float* ssum = smax + 2 * SR_ROWS;                             // [2][64]: a row's sum over the keys of each warp column
     pdl_wait();
@@ -146,26 +147,45 @@ attn_shared_rows_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, 
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
         }
         sr_commit();
+        if (ka < kb) sr_stage_keys(Ks + SR_K_ELEMS, k_store, pt, ka + 1, nkv, kvh);
+        sr_commit();
         for (int kt = ka; kt <= kb; kt++) {
-            const int cur = (kt - ka) & 1;
-            if (kt < kb) sr_stage_keys(Ks + (cur ^ 1) * SR_K_ELEMS, k_store, pt, kt + 1, nkv, kvh);
-            sr_commit();
+            const int cur = (kt - ka) % SR_STAGES;
             sr_wait<1>();
-            __syncthreads();
+            __syncthreads();       // the turn's keys are there, and every warp has left the turn before: its stage is free
+            if (kt + 2 <= kb) sr_stage_keys(Ks + ((kt + 2 - ka) % SR_STAGES) * SR_K_ELEMS, k_store, pt, kt + 2, nkv, kvh);
+            sr_commit();
             const bf16* Kc = Ks + cur * SR_K_ELEMS;
-            float s[2][4];
+            // two chains of sums a key block (even and odd steps of the row's length), so that a product need not wait
+            // for the one before it
+            float s[2][4], s2[2][4];
 #pragma unroll
-            for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
             const bf16* qa = Qs + (wr * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * SR_STR + 8 * (lane >> 4);
             const bf16* ka_ = Kc + (wc * 16 + (lane & 7) + 8 * (lane >> 4)) * SR_STR + 8 * ((lane >> 3) & 1);
-#pragma unroll 4
-            for (int ks = 0; ks < HD / 16; ks++) {
-                uint32_t a[4], b[4];
+#pragma unroll 2
+            for (int ks = 0; ks + 1 < HD / 16; ks += 2) {
+                uint32_t a[4], b[4], a2[4], b2[4];
                 sr_ldsm(a, qa + ks * 16);
                 sr_ldsm(b, ka_ + ks * 16);
+                sr_ldsm(a2, qa + ks * 16 + 16);
+                sr_ldsm(b2, ka_ + ks * 16 + 16);
+                sr_mma(s[0], a, b[0], b[1]);
+                sr_mma(s[1], a, b[2], b[3]);
+                sr_mma(s2[0], a2, b2[0], b2[1]);
+                sr_mma(s2[1], a2, b2[2], b2[3]);
+            }
+            if ((HD / 16) & 1) {
+                uint32_t a[4], b[4];
+                sr_ldsm(a, qa + (HD / 16 - 1) * 16);
+                sr_ldsm(b, ka_ + (HD / 16 - 1) * 16);
                 sr_mma(s[0], a, b[0], b[1]);
                 sr_mma(s[1], a, b[2], b[3]);
             }
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) s[i][c] += s2[i][c];
             const int key0 = kt * SR_KEYS + wc * 16;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -230,7 +250,6 @@ attn_shared_rows_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, 
                     sr_mma(acc[2 * dp + 1], a, b[2], b[3]);
                 }
             }
-            __syncthreads();
         }
     }
     // the row sums of the two warp columns meet
@@ -278,31 +297,40 @@ attn_shared_rows_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, 
     }
 }
 
-// The parts of a split step put together: a warp per (row, head). M = the parts' largest maximum,
-// L = sum_s l_s 2^(m_s - M), out = sum_s acc_s 2^(m_s - M) / L * out_scale (maxima in the log2 domain).
-__global__ void attn_shared_rows_merge_kernel(const float* ws_acc, const float* ws_ml, bf16* out, long long ldo,
-                                              float out_scale, int n_rows, int nh, int nsplit) {
+// The parts of a split step put together: a block per (row, head), a thread per four value columns. M = the parts'
+// largest maximum, w_s = 2^(m_s - M), L = sum_s l_s w_s, out = sum_s acc_s w_s / L * out_scale (maxima in the log2 domain).
+constexpr int SR_MAX_SPLITS = 16;
+__global__ void __launch_bounds__(HDV / 4)
+attn_shared_rows_merge_kernel(const float* __restrict__ ws_acc, const float* __restrict__ ws_ml, bf16* out, long long ldo,
+                              float out_scale, int nh, int nsplit) {
     pdl_wait();
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31;
-    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (wid >= n_rows * nh) return;
-    const int b = wid / nh, h = wid % nh;
-    bf16* o = out + (size_t)b * ldo + (size_t)h * HDV;
-    const float* ml = ws_ml + (size_t)wid * nsplit * 2;
-    const float* acc = ws_acc + (size_t)wid * nsplit * HDV;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; s++) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    if (M != -INFINITY)
-        for (int s = 0; s < nsplit; s++) L += ml[2 * s + 1] * exp2f(ml[2 * s] - M);
-    const float inv = L > 0.f ? out_scale / L : 0.f;
-    for (int d = lane; d < HDV; d += 32) {
-        float a = 0.f;
-        if (L > 0.f)
-            for (int s = 0; s < nsplit; s++) a = fmaf(acc[(size_t)s * HDV + d], exp2f(ml[2 * s] - M), a);
-        o[d] = __float2bfloat16_rn(a * inv);
+    const int b = blockIdx.x / nh, h = blockIdx.x % nh;
+    const float* ml = ws_ml + (size_t)blockIdx.x * nsplit * 2;
+    const float4* acc = reinterpret_cast<const float4*>(ws_acc + (size_t)blockIdx.x * nsplit * HDV) + threadIdx.x;
+    float w[SR_MAX_SPLITS];
+    float M = -INFINITY, L = 0.f;
+#pragma unroll
+    for (int s = 0; s < SR_MAX_SPLITS; s++)
+        if (s < nsplit) M = fmaxf(M, ml[2 * s]);
+#pragma unroll
+    for (int s = 0; s < SR_MAX_SPLITS; s++) {
+        w[s] = (s < nsplit && M != -INFINITY) ? exp2f(ml[2 * s] - M) : 0.f;
+        if (s < nsplit) L += ml[2 * s + 1] * w[s];
     }
+    const float inv = L > 0.f ? out_scale / L : 0.f;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < SR_MAX_SPLITS; s++)
+        if (s < nsplit) {
+            const float4 v = acc[(size_t)s * (HDV / 4)];
+            a.x = fmaf(v.x, w[s], a.x), a.y = fmaf(v.y, w[s], a.y), a.z = fmaf(v.z, w[s], a.z), a.w = fmaf(v.w, w[s], a.w);
+        }
+    uint2 o;
+    o.x = sr_pack(a.x * inv, a.y * inv), o.y = sr_pack(a.z * inv, a.w * inv);
+    bf16* dst = out + (size_t)b * ldo + (size_t)h * HDV + 4 * threadIdx.x;
+    *reinterpret_cast<uint32_t*>(dst) = o.x;
+    *reinterpret_cast<uint32_t*>(dst + 2) = o.y;
 }
 
 // tiles (or null for a single-token step of n_items rows), n_items: tiles or rows. nsplit > 1 only for single tokens.
@@ -311,7 +339,7 @@ DK_EXPORT int dk_attn_shared_rows_bf16(const void* q, long long ldq, void* out, 
                                        const int* seq_pos0, const int* row_pos, const int* page_table, int pt_stride,
                                        int nh, int nkv, int window, int chunk, float scale, int nsplit, float* ws_acc,
                                        float* ws_ml, cudaStream_t st) {
-    if (nh % nkv != 0 || nsplit < 1 || (nsplit > 1 && (tiles != nullptr || ws_acc == nullptr || ws_ml == nullptr)))
+    if (nh % nkv != 0 || nsplit < 1 || nsplit > SR_MAX_SPLITS || (nsplit > 1 && (tiles != nullptr || ws_acc == nullptr || ws_ml == nullptr)))
         return (int)cudaErrorInvalidValue;
     if (ldq % 8 != 0 || ldo % 2 != 0 || ((uintptr_t)q & 15) != 0 || ((uintptr_t)out & 3) != 0) return (int)cudaErrorInvalidValue;
     static bool attr = false;
@@ -324,8 +352,8 @@ DK_EXPORT int dk_attn_shared_rows_bf16(const void* q, long long ldq, void* out, 
                       (const bf16*)q, ldq, (bf16*)out, ldo, out_scale, (const bf16*)k_store, tiles, cu_q, seq_pos0, row_pos,
                       page_table, pt_stride, nh, nkv, window, chunk, scale * 1.4426950408889634f, nsplit, ws_acc, ws_ml);
     if (e != 0 || nsplit == 1) return e;
-    return dk_launch(attn_shared_rows_merge_kernel, dim3((n_items * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
-                     (const float*)ws_ml, (bf16*)out, ldo, out_scale, n_items, nh, nsplit);
+    return dk_launch(attn_shared_rows_merge_kernel, dim3(n_items * nh), dim3(HDV / 4), 0, st, (const float*)ws_acc,
+                     (const float*)ws_ml, (bf16*)out, ldo, out_scale, nh, nsplit);
 }
 
 DK_EXPORT int dk_attn_shared_rows_tile_queries(int group) { return max(1, SR_ROWS / min(group, SR_ROWS)); }

@@ -110,23 +110,29 @@ latent_query_kernel(const T* q, long long ldq, const T* __restrict__ w_uk, T* ou
 // steps whose plain parts go through a library product instead of latent_query.
 template <typename T>
 __global__ void latent_rotate_kernel(const T* q, long long ldq, T* out, long long ldo, const float* __restrict__ cosv,
-                                     const float* __restrict__ sinv, int rot_dims, const int* row_pos, int n_heads,
+                                     const float* __restrict__ sinv, int rot_dims, const int* row_pos, int n_tok, int n_heads,
                                      int dim, int rot_dim, int kv_rank) {
     pdl_wait();
     pdl_launch_dependents();
-    const int t = blockIdx.x;
+    // a thread per (token, head, two neighbouring coordinates of the rotated part; a last single one if rot_dim is odd)
+    const int per_head = (rot_dim + 1) / 2;
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (long long)n_tok * n_heads * per_head) return;
+    const int i = 2 * (int)(item % per_head), h = (int)(item / per_head % n_heads), t = (int)(item / per_head / n_heads);
     const int pos = row_pos[t];
-    const int half = rot_dims / 2;
-    for (int j = threadIdx.x; j < n_heads * rot_dim; j += blockDim.x) {
-        const int h = j / rot_dim, i = j % rot_dim;
-        const T* rq = q + (size_t)t * ldq + (size_t)h * (dim + rot_dim) + dim;
-        float y = pos < 0 ? 0.f : to_f(rq[i]);
-        if (pos >= 0 && i < rot_dims) {
-            const float c = cosv[(size_t)pos * half + i / 2], sn = sinv[(size_t)pos * half + i / 2];
-            y = (i & 1) ? y * c + to_f(rq[i - 1]) * sn : y * c - to_f(rq[i + 1]) * sn;
-        }
-        out[(size_t)t * ldo + (size_t)h * (kv_rank + rot_dim) + kv_rank + i] = from_f<T>(y);
+    const T* rq = q + (size_t)t * ldq + (size_t)h * (dim + rot_dim) + dim;
+    T* o = out + (size_t)t * ldo + (size_t)h * (kv_rank + rot_dim) + kv_rank;
+    const bool two = i + 1 < rot_dim;
+    float u = pos < 0 ? 0.f : to_f(rq[i]), v = (pos < 0 || !two) ? 0.f : to_f(rq[i + 1]);
+    if (pos >= 0 && i + 1 < rot_dims) {
+        const int half = rot_dims / 2;
+        const float c = cosv[(size_t)pos * half + i / 2], sn = sinv[(size_t)pos * half + i / 2];
+        const float u2 = u * c - v * sn;
+        v = v * c + u * sn;
+        u = u2;
     }
+    o[i] = from_f<T>(u);
+    if (two) o[i + 1] = from_f<T>(v);
 }
 
 // One block per (token, head); a warp per output: W_uv's row of kv_rank numbers times the latent output.
@@ -171,8 +177,10 @@ DK_EXPORT int dk_latent_query(int dtype, const void* q, long long ldq, const voi
                               int n_heads, int dim, int rot_dim, int kv_rank, int plain, cudaStream_t st) {
     if (rot_dims % 2 || rot_dims > rot_dim) return (int)cudaErrorInvalidValue;
     if (!plain) {
-        LT_DISPATCH(dtype, return dk_launch(latent_rotate_kernel<T>, dim3(n_tok), dim3(128), 0, st, (const T*)q, ldq,
-                                            (T*)out, ldo, cosv, sinv, rot_dims, row_pos, n_heads, dim, rot_dim, kv_rank));
+        const long long items = (long long)n_tok * n_heads * ((rot_dim + 1) / 2);
+        LT_DISPATCH(dtype, return dk_launch(latent_rotate_kernel<T>, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, st,
+                                            (const T*)q, ldq, (T*)out, ldo, cosv, sinv, rot_dims, row_pos, n_tok, n_heads, dim,
+                                            rot_dim, kv_rank));
     }
     const size_t smem = (size_t)(dim + rot_dim) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;

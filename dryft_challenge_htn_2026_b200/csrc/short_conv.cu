@@ -138,6 +138,108 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
     }
 }
 
+// The same without a convolution (taps = 1): a warp per (token row, head), the head in registers (coordinate
+// lane + 32 i), sums by shuffles, the rotation's partners through the warp's own piece of shared memory. No block
+// barrier; eight heads a block.
+#define SC_ROW_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(32 * SC_ROW_WARPS)
+norm_rope_rows_kernel(const T* proj, long long ld, T* out, long long ldo, int norm_mode, const float* __restrict__ qn,
+                      const float* __restrict__ kn, float eps, const float* __restrict__ vmix, const T* v_src,
+                      long long ld_src, const float* __restrict__ cosv, const float* __restrict__ sinv, int rot_dims,
+                      const int* row_pos, const int* row_seq, int n_tok, int nh, int nkv, int hd, int hdv, T* k_store,
+                      T* v_store, const int* page_table, int pt_stride) {
+    __shared__ float ys_all[SC_ROW_WARPS][256];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = nh + 2 * nkv;
+    const long long item = (long long)blockIdx.x * SC_ROW_WARPS + warp;
+    if (item >= (long long)n_tok * heads) return;
+    const int t = (int)(item / heads), head = (int)(item % heads);
+    const int pos = row_pos[t];
+    if (pos < 0) return;
+    float* ys = ys_all[warp];
+    int c0, size;
+    const float* wn = nullptr;
+    if (head < nh) { c0 = head * hd; size = hd; wn = qn; }
+    else if (head < nh + nkv) { c0 = nh * hd + (head - nh) * hd; size = hd; wn = kn; }
+    else { c0 = (nh + nkv) * hd + (head - nh - nkv) * hdv; size = hdv; }
+    const bool qk = head < nh + nkv;
+    const T* src = proj + (size_t)t * ld + c0;
+    float y[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        y[i] = d < size ? to_f(src[d]) : 0.f;
+        ss += y[i] * y[i];
+    }
+    if (qk && norm_mode == 1) {
+        const float rs = 1.f / sqrtf(warp_sum(ss) / (float)size + eps);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = lane + 32 * i;
+            if (d < size) y[i] *= wn ? rs * wn[d] : rs;
+        }
+    }
+    if (!qk && v_src != nullptr) {
+        const float lam = vmix[0];
+        const T* vs = v_src + (size_t)t * ld_src + (size_t)(head - nh - nkv) * hdv;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = lane + 32 * i;
+            if (d < size) y[i] = (1.f - lam) * y[i] + lam * to_f(vs[d]);
+        }
+    }
+    if (qk && rot_dims > 0) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = lane + 32 * i;
+            if (d < rot_dims) ys[d] = y[i];
+        }
+        __syncwarp();
+        const int half = rot_dims / 2;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = lane + 32 * i;
+            if (d < rot_dims) {
+                const int j = d < half ? d : d - half;
+                const float c = cosv[(size_t)pos * half + j], sn = sinv[(size_t)pos * half + j];
+                y[i] = d < half ? ys[d] * c - ys[d + half] * sn : ys[d] * c + ys[d - half] * sn;
+            }
+        }
+    }
+    if (qk && norm_mode == 2) {
+        ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss += y[i] * y[i];        // coordinates past the head's size are zero
+        const float rs = 1.f / sqrtf(warp_sum(ss) / (float)size + eps);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = lane + 32 * i;
+            if (d < size) y[i] *= wn ? rs * wn[d] : rs;
+        }
+    }
+    T* cached = nullptr;
+    if (k_store != nullptr && head >= nh) {
+        const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
+        if (page >= 0)
+            cached = head < nh + nkv ? k_store + kv_offset(page, nkv, head - nh, pos % DK_PAGE, hd)
+                                     : v_store + kv_offset(page, nkv, head - nh - nkv, pos % DK_PAGE, hdv);
+    }
+    T* dst = out + (size_t)t * ldo + c0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        if (d < size) {
+            const T o = from_f<T>(y[i]);
+            dst[d] = o;
+            if (cached != nullptr) cached[d] = o;
+        }
+    }
+}
+
 // state[slot] <- the last taps - 1 projected rows of the sequence as it stands after this step: rows of
 // this step where it brought enough, the newest of the old state before them where it did not.
 template <typename T>
@@ -171,6 +273,17 @@ DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void*
                                 cudaStream_t st) {
     if (hd > 256 || hdv > 256 || taps < 1 || taps > SC_MAX_TAPS || rot_dims > hd || rot_dims % 2)
         return (int)cudaErrorInvalidValue;
+    if (taps == 1) {
+        const long long items = (long long)n_tok * (nh + 2 * nkv);
+        const dim3 rgrid((unsigned)((items + SC_ROW_WARPS - 1) / SC_ROW_WARPS)), rblock(32 * SC_ROW_WARPS);
+        if (dtype == 0)
+            return dk_launch(norm_rope_rows_kernel<float>, rgrid, rblock, 0, st, (const float*)proj, ld, (float*)out, ldo,
+                             norm_mode, qn, kn, eps, vmix, (const float*)v_src, ld_src, cosv, sinv, rot_dims, row_pos,
+                             row_seq, n_tok, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride);
+        return dk_launch(norm_rope_rows_kernel<bf16>, rgrid, rblock, 0, st, (const bf16*)proj, ld, (bf16*)out, ldo, norm_mode,
+                         qn, kn, eps, vmix, (const bf16*)v_src, ld_src, cosv, sinv, rot_dims, row_pos, row_seq, n_tok, nh,
+                         nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride);
+    }
     const dim3 grid(n_tok, nh + 2 * nkv), block(SC_THREADS);
     if (dtype == 0)
         return dk_launch(conv_norm_rope_kernel<float>, grid, block, 0, st, (const float*)proj, ld, (float*)out, ldo,
