@@ -7,7 +7,8 @@
 //
 // A block of 8 warps owns 64 rows of the (query, head of the group) plane of one sequence and one key/value head:
 // with G heads in a group, 64 / G consecutive queries with all their heads (G >= 64: one query and 64 of its heads).
-// It keeps its 64 query rows in shared memory and walks the keys in half pages of 32, staged by cp.async three deep:
+// It keeps its 64 query rows in shared memory and walks the keys in half pages of 32, staged by cp.async (three stages:
+// the half page whose scores are taken, the one before it, whose P.V runs side by side with them, and the one on its way):
 //   scores : warp (r, c) takes rows 16 r .. 16 r + 15 against keys 16 c .. 16 c + 15 of the half page, query and key
 //            fragments by ldmatrix, mma.sync m16n8k16; the two warps of a row block meet their row maxima in shared
 //            memory and leave P there;
@@ -74,6 +75,49 @@ __device__ __forceinline__ void sr_stage_keys(bf16* stage, const bf16* k_store, 
     for (int c = threadIdx.x; c < SR_KEYS * CK; c += SR_THREADS) {
         const int row = c / CK, col = (c % CK) * 8;
         sr_cp16(stage + row * SR_STR + col, k_store + off + (size_t)row * HD + col);
+    }
+}
+
+// The products of a turn, the two kinds step by step in turn so that neither waits for its own loads: SCORES: s +=
+// (16 query rows at qa) x (16 keys at kc) over the row's length, in two chains of sums (even and odd steps); PV: acc +=
+// (P of 16 rows x 32 keys at pa) x (this warp's value columns of those 32 rows at vp).
+template <bool SCORES, bool PV>
+__device__ __forceinline__ void sr_products(const bf16* qa, const bf16* kc, const bf16* pa, const bf16* vp, float (&s)[2][4],
+                                            float (&acc)[SR_HALF / 8][4]) {
+    constexpr int DPN = SR_HALF / 16;
+    constexpr int N1 = SCORES ? HD / 16 : 0, N2 = PV ? (SR_KEYS / 16) * DPN : 0;
+    float s2[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++) s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
+    uint32_t pf[4];
+#pragma unroll
+    for (int i = 0; i < (N1 > N2 ? N1 : N2); i++) {
+        if (i < N1) {
+            uint32_t a[4], b[4];
+            sr_ldsm(a, qa + i * 16);
+            sr_ldsm(b, kc + i * 16);
+            if (i & 1) {
+                sr_mma(s2[0], a, b[0], b[1]);
+                sr_mma(s2[1], a, b[2], b[3]);
+            } else {
+                sr_mma(s[0], a, b[0], b[1]);
+                sr_mma(s[1], a, b[2], b[3]);
+            }
+        }
+        if (i < N2) {
+            const int kk = i / DPN, dp = i % DPN;
+            if (dp == 0) sr_ldsm(pf, pa + kk * 16);
+            uint32_t b[4];
+            sr_ldsm_trans(b, vp + kk * 16 * SR_STR + dp * 16);
+            sr_mma(acc[2 * dp], pf, b[0], b[1]);
+            sr_mma(acc[2 * dp + 1], pf, b[2], b[3]);
+        }
+    }
+    if (SCORES) {
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) s[i][c] += s2[i][c];
     }
 }
 
@@ -147,63 +191,47 @@ attn_shared_rows_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, 
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
         }
         sr_commit();
-        if (ka < kb) sr_stage_keys(Ks + SR_K_ELEMS, k_store, pt, ka + 1, nkv, kvh);
-        sr_commit();
-        for (int kt = ka; kt <= kb; kt++) {
-            const int cur = (kt - ka) % SR_STAGES;
-            sr_wait<1>();
-            __syncthreads();       // the turn's keys are there, and every warp has left the turn before: its stage is free
-            if (kt + 2 <= kb) sr_stage_keys(Ks + ((kt + 2 - ka) % SR_STAGES) * SR_K_ELEMS, k_store, pt, kt + 2, nkv, kvh);
+        const bf16* qa = Qs + (wr * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * SR_STR + 8 * (lane >> 4);
+        const bf16* pa = Ps + (wr * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * SR_PSTR + 8 * (lane >> 4);
+        const int k_lane = (wc * 16 + (lane & 7) + 8 * (lane >> 4)) * SR_STR + 8 * ((lane >> 3) & 1);
+        const int v_lane = (lane & 15) * SR_STR + wc * SR_HALF + 8 * (lane >> 4);
+        // Turn kt takes the scores of half page kt and, side by side with them, P.V of half page kt - 1 (whose P the turn
+        // before left in shared memory): two independent streams of products for every warp. One more turn ends it.
+        for (int kt = ka; kt <= kb + 1; kt++) {
+            sr_wait<0>();
+            __syncthreads();       // half page kt is there; every warp has left the turn before, so the stage of kt - 2 is free
+            if (kt + 1 <= kb) sr_stage_keys(Ks + ((kt + 1 - ka) % SR_STAGES) * SR_K_ELEMS, k_store, pt, kt + 1, nkv, kvh);
             sr_commit();
-            const bf16* Kc = Ks + cur * SR_K_ELEMS;
-            // two chains of sums a key block (even and odd steps of the row's length), so that a product need not wait
-            // for the one before it
-            float s[2][4], s2[2][4];
+            const bf16* Kc = Ks + ((kt - ka) % SR_STAGES) * SR_K_ELEMS;
+            const bf16* Kp = Ks + ((kt - ka + SR_STAGES - 1) % SR_STAGES) * SR_K_ELEMS;
+            const bool scores = kt <= kb;
+            float s[2][4];
 #pragma unroll
-            for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
-            const bf16* qa = Qs + (wr * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * SR_STR + 8 * (lane >> 4);
-            const bf16* ka_ = Kc + (wc * 16 + (lane & 7) + 8 * (lane >> 4)) * SR_STR + 8 * ((lane >> 3) & 1);
-#pragma unroll 2
-            for (int ks = 0; ks + 1 < HD / 16; ks += 2) {
-                uint32_t a[4], b[4], a2[4], b2[4];
-                sr_ldsm(a, qa + ks * 16);
-                sr_ldsm(b, ka_ + ks * 16);
-                sr_ldsm(a2, qa + ks * 16 + 16);
-                sr_ldsm(b2, ka_ + ks * 16 + 16);
-                sr_mma(s[0], a, b[0], b[1]);
-                sr_mma(s[1], a, b[2], b[3]);
-                sr_mma(s2[0], a2, b2[0], b2[1]);
-                sr_mma(s2[1], a2, b2[2], b2[3]);
-            }
-            if ((HD / 16) & 1) {
-                uint32_t a[4], b[4];
-                sr_ldsm(a, qa + (HD / 16 - 1) * 16);
-                sr_ldsm(b, ka_ + (HD / 16 - 1) * 16);
-                sr_mma(s[0], a, b[0], b[1]);
-                sr_mma(s[1], a, b[2], b[3]);
-            }
-#pragma unroll
-            for (int i = 0; i < 2; i++)
-#pragma unroll
-                for (int c = 0; c < 4; c++) s[i][c] += s2[i][c];
-            const int key0 = kt * SR_KEYS + wc * 16;
+            for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            if (scores && kt > ka) sr_products<true, true>(qa, Kc + k_lane, pa, Kp + v_lane, s, acc);
+            else if (scores) sr_products<true, false>(qa, Kc + k_lane, pa, Kp + v_lane, s, acc);
+            else sr_products<false, true>(qa, Kc + k_lane, pa, Kp + v_lane, s, acc);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (scores) {
+                const int key0 = kt * SR_KEYS + wc * 16;
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
+                for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int key = key0 + nt * 8 + 2 * t + (c & 1), r = c >> 1;
-                    const float v = (key >= lo[r] && key <= hi[r]) ? s[nt][c] * sl2 : -INFINITY;
-                    s[nt][c] = v;
-                    mx[r] = fmaxf(mx[r], v);
+                    for (int c = 0; c < 4; c++) {
+                        const int key = key0 + nt * 8 + 2 * t + (c & 1), r = c >> 1;
+                        const float v = (key >= lo[r] && key <= hi[r]) ? s[nt][c] * sl2 : -INFINITY;
+                        s[nt][c] = v;
+                        mx[r] = fmaxf(mx[r], v);
+                    }
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    if (t == 0) smax[wc * SR_ROWS + wr * 16 + g + 8 * r] = mx[r];
                 }
-#pragma unroll
-            for (int r = 0; r < 2; r++) {
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                if (t == 0) smax[wc * SR_ROWS + wr * 16 + g + 8 * r] = mx[r];
             }
-            __syncthreads();
+            __syncthreads();       // the maxima of both warp columns are there; P of the turn before has been read
+            if (!scores) break;
             float ms[2], alpha[2], sum[2] = {0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < 2; r++) {
@@ -234,21 +262,6 @@ attn_shared_rows_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, 
                 acc[i][1] *= alpha[0];
                 acc[i][2] *= alpha[1];
                 acc[i][3] *= alpha[1];
-            }
-            __syncthreads();
-            const bf16* pa = Ps + (wr * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * SR_PSTR + 8 * (lane >> 4);
-            const bf16* va = Kc + (lane & 15) * SR_STR + wc * SR_HALF + 8 * (lane >> 4);
-#pragma unroll
-            for (int kk = 0; kk < SR_KEYS / 16; kk++) {
-                uint32_t a[4];
-                sr_ldsm(a, pa + kk * 16);
-#pragma unroll
-                for (int dp = 0; dp < SR_HALF / 16; dp++) {
-                    uint32_t b[4];
-                    sr_ldsm_trans(b, va + kk * 16 * SR_STR + dp * 16);
-                    sr_mma(acc[2 * dp], a, b[0], b[1]);
-                    sr_mma(acc[2 * dp + 1], a, b[2], b[3]);
-                }
             }
         }
     }
