@@ -28,10 +28,13 @@ class QueryTiles(StepPlan):
     def build(self, lens, pos0, is_decode):
         if is_decode:
             return np.zeros((0, 2), np.int32)
-        tiles = [(int(pos0[i]) + min(q0 + self.rows, int(lens[i])), i, q0)
-                 for i in range(len(lens)) for q0 in range(0, int(lens[i]), self.rows)]
-        tiles.sort(key=lambda t: -t[0])
-        return np.array([(t[1], t[2]) for t in tiles], dtype=np.int32).reshape(-1, 2)
+        lens, pos0 = np.asarray(lens, dtype=np.int64), np.asarray(pos0, dtype=np.int64)
+        per_seq = (lens + self.rows - 1) // self.rows                      # tiles of each sequence
+        seq = np.repeat(np.arange(len(lens), dtype=np.int64), per_seq)
+        q0 = (np.arange(int(per_seq.sum()), dtype=np.int64) - np.repeat(np.cumsum(per_seq) - per_seq, per_seq)) * self.rows
+        last_key = pos0[seq] + np.minimum(q0 + self.rows, lens[seq])
+        order = np.argsort(-last_key, kind="stable")                       # ties stay in (sequence, first query) order
+        return np.stack([seq[order], q0[order]], 1).astype(np.int32).reshape(-1, 2)
 
 
 class GQAAttention(Part):

@@ -4,6 +4,7 @@ consistency."""
 import copy
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -143,3 +144,22 @@ def test_plain_model_sees_what_the_masks_allow():
     near = list(tokens)
     near[52] = 77
     assert float((plain.forward(cfg, t, near)[59] - base[59]).abs().max()) > 1e-6
+
+
+def test_plans_of_the_kernel_for_rows_that_are_key_and_value():
+    """Which sizes the kernel takes, how many queries a block of 64 (query, head) rows holds, how a single token's keys
+    are dealt out, and the vectorised list of query tiles (most keys first, ties in sequence order)."""
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.parts.attention import QueryTiles
+    assert api.shared_rows_takes(576, 512) and api.shared_rows_takes(336, 320) and api.shared_rows_takes(32, 32)
+    assert not api.shared_rows_takes(80, 48) and not api.shared_rows_takes(648, 512) and not api.shared_rows_takes(320, 336)
+    assert [api.shared_rows_tile_queries(g) for g in (1, 3, 32, 64, 70, 128)] == [64, 21, 2, 1, 1, 1]
+    sms = api.sm_count()
+    assert api.shared_rows_splits(sms, 32, 1, 40, 1024, None) == 1                         # a block an SM already
+    assert api.shared_rows_splits(1, 32, 1, 40, None, 64) == 2                             # a chunk of two half pages (and the ragged one)
+    assert api.shared_rows_splits(1, 32, 1, 400, None, None) == api.SHARED_ROWS_MAX_SPLITS
+    assert api.shared_rows_splits(1, 128, 1, 400, None, None) == min(api.SHARED_ROWS_MAX_SPLITS, sms // 2)   # two blocks of heads a token
+    tiles = QueryTiles(21).build(np.array([50, 1, 30]), np.array([0, 70, 40]), False)
+    assert tiles.dtype == np.int32
+    assert tiles.tolist() == [[1, 0], [2, 21], [2, 0], [0, 42], [0, 21], [0, 0]]           # last keys 71, 70, 61, 50, 42, 21
+    assert QueryTiles(21).build(np.array([1, 1]), np.array([5, 6]), True).shape == (0, 2)
