@@ -719,7 +719,9 @@ def venidra_kernel_times(torch, dk, pk, cfg_d, heads, kv_heads):
     def fill(cache, n):
         for e in range(n):
             v = cache.views(e)[0]
-            v.k.normal_(), v.v.normal_()
+            v.k.normal_()
+            if v.v is not None:
+                v.v.normal_()
 
     def steps(ctx, cache, rows, tag, keys_att, keys_lat, pairs_att, pairs_lat, pairs_full):
         """One record per step of the two mixers; ``pairs_*``: (query, key) pairs in sight, ``keys_*``: keys a row reads."""
@@ -740,7 +742,7 @@ def venidra_kernel_times(torch, dk, pk, cfg_d, heads, kv_heads):
         table = ctx.tables[l_views[0].group]
         us = timed(lambda: api.latent_norm_rope_write(down, cq, lat.q_norm_w, lat.kv_norm_w, ls.norm_eps, cos, sin, rot, ctx.row_pos,
                                                       ctx.row_seq, Qr, L, R, l_views[0].k, l_views[0].v, table))
-        out[f"latent_norms_rotation_cache_write_{tag}"] = bytes_rec(us, rows * (lat.n_down + Qr + 2 * L + R) * 2)
+        out[f"latent_norms_rotation_cache_write_{tag}"] = bytes_rec(us, rows * (lat.n_down + Qr + L + R) * 2)
         qu = torch.randn(rows, lat.n_q, device=dev).to(bf)
         ql = lat.queries(ctx, qu)
         us = timed(lambda: lat.queries(ctx, qu))

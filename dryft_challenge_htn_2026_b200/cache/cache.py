@@ -40,7 +40,14 @@ class KVGroup:
         self.first = {}                                   # slot -> index of the first page not yet given back
         self.store = self.v_store = None
         vd = request.v_head_dim
-        if allocate and (vd is None or vd == request.head_dim):
+        self.keys_only = bool(request.values_in_keys)
+        if self.keys_only:
+            if vd is None or vd > request.head_dim:
+                raise ValueError(f"values of {vd} numbers inside key rows of {request.head_dim}")
+            if allocate:
+                self.store = torch.zeros((len(self.entries), num_pages, request.n_kv_heads, PAGE, request.head_dim),
+                                         dtype=request.dtype, device=device)
+        elif allocate and (vd is None or vd == request.head_dim):
             self.store = torch.zeros((len(self.entries), 2, num_pages, request.n_kv_heads, PAGE, request.head_dim),
                                      dtype=request.dtype, device=device)
         elif allocate:    # keys and values of different sizes: a store each, [entries, pages, n_kv, PAGE, size]
@@ -51,6 +58,8 @@ class KVGroup:
 
     def view(self, entry):
         e = self.entries.index(entry)
+        if self.keys_only:
+            return KVView(self.index, self.store[e], None)
         if self.v_store is not None:
             return KVView(self.index, self.store[e], self.v_store[e])
         return KVView(self.index, self.store[e, 0], self.store[e, 1])

@@ -13,7 +13,8 @@ class KVRequest:
     ``chunk``: a token reads only keys of its own chunk of that many positions (counted from the
     sequence's start), so pages wholly before the chunk of the next token may be given back.
     ``keep_first``: the first that many positions stay in sight whatever the window or chunk: their pages
-    are never given back."""
+    are never given back. ``values_in_keys``: a token's value row is the first ``v_head_dim`` numbers of its key row
+    (rows of latents): there is no store of values, and a view's ``v`` is None."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int]
@@ -21,6 +22,7 @@ class KVRequest:
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
     keep_first: int = 0
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

@@ -104,8 +104,9 @@ class MaskedAttentionSpec:
     ``value_mix``: the layers of a model that say it share the values of the first of them ("source": it leaves its
     values of the step's tokens for the others and caches them as they are); every other ("blend") caches and uses
     v <- (1 - lam) v + lam v_source with its learned number ``vmix`` (both kinds hold the tensor; the source's is unused).
-    ``values_in_keys``: whoever fills the cache makes a value row the first ``v_head_dim`` numbers of its key row (the rows of
-    latents of an attention through latents), so a kernel may read the key rows alone."""
+    ``values_in_keys``: a token's value row is the first ``v_head_dim`` numbers of its key row (the rows of latents of an
+    attention through latents): the cache keeps the key rows alone and every kernel reads values from them (the tcgen05 prompt
+    kernel and the split single-token kernel, which want a store of values, are not used then)."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int

@@ -1128,7 +1128,8 @@ def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos,
         raise KernelError("conv_norm_rope: shapes do not match")
     if k_store is not None:
         _need(k_store, "k_store", proj.dtype, 4), _need(v_store, "v_store", proj.dtype, 4), _need(page_table, "page_table", torch.int32, 2)
-        if k_store.shape[1:] != (n_kv_heads, PAGE, head_dim) or v_store.shape[1:] != (n_kv_heads, PAGE, v_head_dim):
+        if k_store.shape[1:] != (n_kv_heads, PAGE, head_dim) or \
+                (v_store is not None and v_store.shape[1:] != (n_kv_heads, PAGE, v_head_dim)):
             raise KernelError("conv_norm_rope: key/value stores of the wrong shape")
     lib = _lib("short_conv.cu")
     _check(lib, lib.dk_conv_norm_rope(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(out), c_longlong(out.stride(0)),
@@ -1158,7 +1159,8 @@ def latent_norm_rope_write(proj, cq_out, q_norm_w, kv_norm_w, eps, cos, sin, rot
     """Rows [a (q_rank) | b (kv_rank) | r (rot_dim)] of a fused down projection: cq_out = rmsnorm(a) * q_norm_w;
     rmsnorm(b) * kv_norm_w and r, its first ``rot_dims`` coordinates rotated by neighbouring pairs (cos/sin
     [positions, rot_dims/2]), go to each token's place in the paged cache of one kv head: key row [c | r]
-    (k_store [pages, 1, PAGE, kv_rank + rot_dim]), value row c (v_store [pages, 1, PAGE, kv_rank])."""
+    (k_store [pages, 1, PAGE, kv_rank + rot_dim]), and, where the cache keeps a store of values, value row c
+    (v_store [pages, 1, PAGE, kv_rank] or None)."""
     _need_rows(proj, "proj"), _need_rows(cq_out, "cq_out", proj.dtype)
     _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(kv_norm_w, "kv_norm_w", torch.float32, 1)
     _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
@@ -1169,7 +1171,7 @@ def latent_norm_rope_write(proj, cq_out, q_norm_w, kv_norm_w, eps, cos, sin, rot
         raise KernelError("latent_norm_rope_write: shapes do not match")
     if k_store is not None:
         _need(k_store, "k_store", proj.dtype, 4), _need(v_store, "v_store", proj.dtype, 4), _need(page_table, "page_table", torch.int32, 2)
-        if k_store.shape[1:] != (1, PAGE, kv_rank + rot_dim) or v_store.shape[1:] != (1, PAGE, kv_rank):
+        if k_store.shape[1:] != (1, PAGE, kv_rank + rot_dim) or (v_store is not None and v_store.shape[1:] != (1, PAGE, kv_rank)):
             raise KernelError("latent_norm_rope_write: key/value stores of the wrong shape")
     lib = _lib("latent.cu")
     _check(lib, lib.dk_latent_norm_rope_write(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(cq_out), c_longlong(cq_out.stride(0)),

@@ -28,6 +28,7 @@ __global__ void kv_write_kernel(const T* k, const T* v, long long ld, T* k_store
     const int in_page = pos % DK_PAGE;
     for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x)
         k_store[kv_offset(page, nkv, i / hd, in_page, hd) + i % hd] = k[(size_t)t * ld + i];
+    if (v_store == nullptr) return;        // values are the key rows' first numbers: nothing of their own to store
     for (int i = threadIdx.x; i < nkv * hdv; i += blockDim.x)
         v_store[kv_offset(page, nkv, i / hdv, in_page, hdv) + i % hdv] = v[(size_t)t * ld + i];
 }
@@ -72,7 +73,7 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
         const int j = jj < lo ? jj - (lo - kept) : jj;
         const int page = pt[j / DK_PAGE];
         const T* kr = k_store + kv_offset(page, nkv, kvh, j % DK_PAGE, hd);
-        const T* vr = v_store + kv_offset(page, nkv, kvh, j % DK_PAGE, hdv);
+        const T* vr = v_store != nullptr ? v_store + kv_offset(page, nkv, kvh, j % DK_PAGE, hdv) : kr;   // no store of values: the key row's start
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < NR; i++) {

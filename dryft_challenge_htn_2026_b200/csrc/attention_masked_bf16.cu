@@ -34,9 +34,11 @@ __device__ __forceinline__ void stage_page_kv(bf16* stage, const bf16* k_store, 
         const int row = c / CK, col = (c % CK) * 8;
         cp_async16(stage + row * KSTR + col, k_store + koff + (size_t)row * HD + col);
     }
+    // without a store of values (v_store null) a value row is the first HDV numbers of its key row
     for (int c = threadIdx.x; c < DK_PAGE * CV; c += blockDim.x) {
         const int row = c / CV, col = (c % CV) * 8;
-        cp_async16(stage + KTILE + row * VSTR + col, v_store + voff + (size_t)row * HDV + col);
+        cp_async16(stage + KTILE + row * VSTR + col,
+                   v_store != nullptr ? v_store + voff + (size_t)row * HDV + col : k_store + koff + (size_t)row * HD + col);
     }
 }
 
@@ -270,8 +272,9 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
         const int page = pt[pos / DK_PAGE];
         for (int i = tid; i < HD; i += MD_THREADS)
             k_out[kv_offset(page, nkv, kvh, pos % DK_PAGE, HD) + i] = k_new[(size_t)b * ldkv + (size_t)kvh * HD + i];
-        for (int i = tid; i < HDV; i += MD_THREADS)
-            v_out[kv_offset(page, nkv, kvh, pos % DK_PAGE, HDV) + i] = v_new[(size_t)b * ldkv + (size_t)kvh * HDV + i];
+        if (v_out != nullptr)
+            for (int i = tid; i < HDV; i += MD_THREADS)
+                v_out[kv_offset(page, nkv, kvh, pos % DK_PAGE, HDV) + i] = v_new[(size_t)b * ldkv + (size_t)kvh * HDV + i];
     }
     for (int i = tid; i < G * HD; i += MD_THREADS) qs[i] = __bfloat162float(q[(size_t)b * ldq + (size_t)kvh * G * HD + i]);
     __syncthreads();
@@ -348,7 +351,8 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
             for (int jj = ks; jj < n; jj += KS) {
                 const int j = lo + jj;
                 const uint4 raw = *reinterpret_cast<const uint4*>(
-                    v_store + kv_offset(pt[j / DK_PAGE], nkv, kvh, j % DK_PAGE, HDV) + cgp * 8);
+                    (v_store != nullptr ? v_store + kv_offset(pt[j / DK_PAGE], nkv, kvh, j % DK_PAGE, HDV)
+                                        : k_store + kv_offset(pt[j / DK_PAGE], nkv, kvh, j % DK_PAGE, HD)) + cgp * 8);
                 const bf16* v8 = reinterpret_cast<const bf16*>(&raw);
                 float vf[8];
 #pragma unroll

@@ -2,7 +2,8 @@
 // projection leaves a row [a | b | r]: a (q_rank numbers) becomes the query latent, b (kv_rank) the key/value
 // latent, r (rot_dim) the one rotated key part that all heads share.
 //   latent_norm_rope_write : c_q = rmsnorm(a) * w_q -> dense rows; c = rmsnorm(b) * w_kv and r rotated by pairs
-//                            -> the token's place in the paged cache: key row [c | r], value row c (one kv head).
+//                            -> the token's place in the paged cache: key row [c | r] (one kv head), whose first kv_rank
+//                            numbers are the value row (a cache with a store of values gets c there as well).
 //   latent_query           : per (token, head) the query of the up projection [plain (dim) | rot (rot_dim)] becomes
 //                            [W_uk_h^T plain (kv_rank) | rot rotated by pairs]: the plain key's up projection moved to
 //                            the query's side, so that scores are taken against the cached latent itself.
@@ -51,11 +52,11 @@ latent_norm_rope_write_kernel(const T* proj, long long ld, T* cq_out, long long 
     ss = block_sum(ss, red);
     const float rs = 1.f / sqrtf(ss / (float)kv_rank + eps);
     T* kr = k_store + kv_offset(page, 1, 0, pos % DK_PAGE, kv_rank + rot_dim);
-    T* vr = v_store + kv_offset(page, 1, 0, pos % DK_PAGE, kv_rank);
+    T* vr = v_store != nullptr ? v_store + kv_offset(page, 1, 0, pos % DK_PAGE, kv_rank) : nullptr;   // a store of values, if the cache keeps one
     for (int i = threadIdx.x; i < kv_rank; i += LT_THREADS) {
         const T c = from_f<T>(to_f(b[i]) * rs * wkv[i]);
         kr[i] = c;
-        vr[i] = c;
+        if (vr != nullptr) vr[i] = c;
     }
     const T* r = b + kv_rank;
     const int half = rot_dims / 2;

@@ -123,7 +123,7 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
     T* cached = nullptr;
     if (k_store != nullptr && head >= nh) {
         const int page = page_table[(size_t)s * pt_stride + pos / DK_PAGE];
-        if (page >= 0)
+        if (page >= 0 && (head < nh + nkv || v_store != nullptr))      // no store of values: only the keys are cached
             cached = head < nh + nkv ? k_store + kv_offset(page, nkv, head - nh, pos % DK_PAGE, hd)
                                      : v_store + kv_offset(page, nkv, head - nh - nkv, pos % DK_PAGE, hdv);
     }
@@ -224,7 +224,7 @@ norm_rope_rows_kernel(const T* proj, long long ld, T* out, long long ldo, int no
     T* cached = nullptr;
     if (k_store != nullptr && head >= nh) {
         const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
-        if (page >= 0)
+        if (page >= 0 && (head < nh + nkv || v_store != nullptr))      // no store of values: only the keys are cached
             cached = head < nh + nkv ? k_store + kv_offset(page, nkv, head - nh, pos % DK_PAGE, hd)
                                      : v_store + kv_offset(page, nkv, head - nh - nkv, pos % DK_PAGE, hdv);
     }

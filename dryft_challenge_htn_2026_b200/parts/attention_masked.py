@@ -32,6 +32,8 @@ class MaskedAttention(Part):
             raise ValueError(f"attention kernels take head sizes up to {api.MASKED_MAX_HEAD}, not {s.head_dim} / {s.v_head_dim}")
         if s.chunk is not None and s.chunk < 1:
             raise ValueError(f"a chunk of {s.chunk} positions")
+        if s.values_in_keys and s.v_head_dim > s.head_dim:
+            raise ValueError(f"values of {s.v_head_dim} numbers cannot be the start of key rows of {s.head_dim}")
         self.n_q, self.n_k = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         self.n_v, self.n_mid = s.num_kv_heads * s.v_head_dim, s.num_heads * s.v_head_dim
         self.n_in = self.n_q + self.n_k + self.n_v + (self.n_mid if s.output_gate else 0)
@@ -71,7 +73,7 @@ class MaskedAttention(Part):
         self.row_tiles = QueryTiles(api.shared_rows_tile_queries(s.num_heads // s.num_kv_heads)) if self.shared_rows else None
         # equal head sizes of 64 or 128: prompts run on the tcgen05 kernel (its masked build), in tiles of 128 queries
         self.tc_tiles = QueryTiles(api.TC_TILE_ROWS) if self.tensor_core and s.head_dim == s.v_head_dim \
-            and s.head_dim in api.TC_ATTENTION_HEAD_DIMS else None
+            and s.head_dim in api.TC_ATTENTION_HEAD_DIMS and not s.values_in_keys else None
 
     def step_plans(self):
         return [t for t in (self.tiles, self.tc_tiles, self.row_tiles) if t is not None]
@@ -121,7 +123,7 @@ class MaskedAttention(Part):
 
     def cache_requests(self):
         s = self.spec
-        r = [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype, s.v_head_dim, s.chunk, s.keep_first)]
+        r = [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype, s.v_head_dim, s.chunk, s.keep_first, s.values_in_keys)]
         if self.taps > 1:     # the convolution's memory: the last taps - 1 projected rows [q | k | v] of a sequence
             r.append(StateRequest((self.taps - 1, self.n_qkv), self.rt.dtype))
         return r
@@ -184,7 +186,8 @@ class MaskedAttention(Part):
         s = self.spec
         table = ctx.tables[kv.group]
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
-        if self.tensor_core and ctx.is_decode and api.masked_decode_streams(q, mid, gate, s.head_dim, s.v_head_dim):
+        if self.tensor_core and ctx.is_decode and not s.values_in_keys \
+                and api.masked_decode_streams(q, mid, gate, s.head_dim, s.v_head_dim):
             # single tokens, keys and values of one size: the library's split decode kernel in its masked build
             if writes:
                 api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)

@@ -69,7 +69,7 @@ class LatentAttention(Part):
 
     def cache_requests(self):
         s = self.spec
-        return [KVRequest(1, self.lat, s.window, self.rt.dtype, s.kv_rank, s.chunk)]
+        return [KVRequest(1, self.lat, s.window, self.rt.dtype, s.kv_rank, s.chunk, values_in_keys=True)]
 
     def prepare(self, max_positions):
         self.max_positions = max_positions

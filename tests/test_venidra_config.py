@@ -104,8 +104,13 @@ def test_tensor_names_and_shapes():
 def test_a_token_holds_one_row_of_latents_and_pages_behind_the_mask_go_back():
     model = CausalLM(dk.config_from_dict(BASE).to_spec(), torch.float32, "cpu")
     reqs = model.entry_requests()
-    assert reqs[0] == reqs[3] == [KVRequest(1, 18, 9, torch.float32, 14, None)]            # key row [latent | rotated part], value row the latent
+    # key row [latent | rotated part]; the value row is its start, so the cache keeps no values of its own
+    assert reqs[0] == reqs[3] == [KVRequest(1, 18, 9, torch.float32, 14, None, 0, True)]
     assert reqs[1] == reqs[2] == reqs[4] == [KVRequest(2, 16, None, torch.float32, 8, 20)]
+    held = Cache(reqs, 64 * 8, 2, "cpu")
+    per_token = [g.bytes() // (len(g.entries) * held.num_pages * 64) for g in held.groups]
+    assert sorted(per_token) == [4 * 18, 4 * 2 * (16 + 8)], per_token                     # 18 numbers a token and latent layer
+    assert all(held.views(e)[0].v is None for e in (0, 3)) and held.views(1)[0].v is not None
     cache = Cache(reqs, 64 * 8, 2, "cpu", allocate=False)
     s = cache.begin()
     cache.reserve(s, 200)

@@ -274,7 +274,11 @@ def test_attention_under_a_chunk_mask_or_a_window(dtype, H, G, D, V, chunk, wind
 # dealt out to several blocks)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,V,chunk,window", [(6, 2, 320, 288, None, 33), (70, 1, 272, 32, 50, None), (3, 3, 288, 288, None, None),
-                                                  (32, 1, 576, 512, None, 100)])
+                                                  (32, 1, 576, 512, None, 100),
+                                                  # narrower rows: the kernels that otherwise read a store of values (mma.sync
+                                                  # prompts and single tokens, float32 arithmetic) take them from the key rows
+                                                  (8, 1, 80, 64, None, 40), (4, 2, 32, 16, 24, None), (3, 1, 20, 10, None, 7),
+                                                  (2, 2, 64, 64, 100, None)])
 def test_attention_over_rows_that_are_key_and_value(dtype, H, G, D, V, chunk, window):
     got, ref = attention_case(dtype, H, G, D, V, chunk, window, [131, 2, 1, 1, 40, 1, 1, 1, 90], values_in_keys=True)
     close(got, ref, dtype, "attention over shared rows")
