@@ -1,5 +1,6 @@
 """A small model library with generation for one NVIDIA B200 (sm_100a): the Qwen3 dense decoder and the
-Nilivik decoder (chunked attention beside linear attention, looped layers).
+Nilivik, Pibulix, Venidra and Nevotar decoders (softmax attention in several forms, linear recurrences, state-space
+mixers, mixtures of experts, looped and shared layers).
 
     from dryft_challenge_htn_2026_b200 import Engine
     eng = Engine("/path/to/model", dtype="bfloat16")
@@ -12,7 +13,7 @@ blocks (``parts``), the paged cache (``cache``), the step function, generation l
 point (``engine``), sampling (``sampling``) and the CUDA kernels (``csrc``).
 """
 from .cache import Cache, CacheFull, KVRequest, StateRequest
-from .config import ConfigError, ModelConfig, ModelSpec, NilivikConfig, PibulixConfig, Qwen3Config
+from .config import ConfigError, ModelConfig, ModelSpec, NevotarConfig, NilivikConfig, PibulixConfig, Qwen3Config
 from .engine import CausalLM, Engine, Runner, load_model, random_model
 from .parts import Part, register_part
 from .registry import architectures, config_from_dict, config_from_folder, register_architecture
@@ -20,7 +21,7 @@ from .sampling import SamplingParams
 from .weights import WeightError, load_weights, write_random_model
 
 __all__ = ["Cache", "CacheFull", "KVRequest", "StateRequest", "ConfigError", "ModelConfig", "ModelSpec", "NilivikConfig", "PibulixConfig",
-           "Qwen3Config",
+           "Qwen3Config", "NevotarConfig",
            "CausalLM", "Engine", "Runner", "load_model", "random_model", "Part", "register_part", "architectures",
            "config_from_dict", "config_from_folder", "register_architecture", "SamplingParams", "WeightError",
            "load_weights", "write_random_model"]

@@ -3,8 +3,10 @@ architecture's own config.json reader."""
 from .specs import (AttentionSpec, DenseMLPSpec, GatedLinearAttentionSpec, GatedMLPSpec, LayerSpec, LinearAttentionSpec,
                     MaskedAttentionSpec, ModelSpec, OnePlusRMSNormSpec, ParallelMixerSpec, PostNormLayerSpec, RMSNormSpec,
                     RotaryHalfSpec, RotaryPairsSpec, RotaryPartSpec, RoutedMLPSpec, SandwichLayerSpec, ScalarRMSNormSpec, ScheduleEntry,
-                    SinusoidSpec, UnitRMSNormSpec, LatentAttentionSpec)
+                    SinusoidSpec, UnitRMSNormSpec, LatentAttentionSpec, DiffAttentionSpec, GroupRMSNormSpec,
+                    LowerBoundRecurrenceSpec, StateSpaceSpec)
 from .base import ConfigError, ModelConfig
+from .nevotar import NevotarConfig
 from .nilivik import NilivikConfig
 from .pibulix import PibulixConfig
 from .qwen3 import Qwen3Config
@@ -14,4 +16,5 @@ __all__ = ["AttentionSpec", "DenseMLPSpec", "GatedMLPSpec", "LayerSpec", "Linear
            "ModelSpec", "ParallelMixerSpec", "RMSNormSpec", "RotaryHalfSpec", "ScalarRMSNormSpec", "ScheduleEntry",
            "SinusoidSpec", "ConfigError", "ModelConfig", "NilivikConfig", "Qwen3Config", "PibulixConfig",
            "GatedLinearAttentionSpec", "OnePlusRMSNormSpec", "PostNormLayerSpec", "RotaryPartSpec", "RoutedMLPSpec", "VenidraConfig", "LatentAttentionSpec", "RotaryPairsSpec",
-           "SandwichLayerSpec", "UnitRMSNormSpec"]
+           "SandwichLayerSpec", "UnitRMSNormSpec", "NevotarConfig", "DiffAttentionSpec", "GroupRMSNormSpec",
+           "LowerBoundRecurrenceSpec", "StateSpaceSpec"]

@@ -41,6 +41,17 @@ class UnitRMSNormSpec:
 
 
 @dataclass(frozen=True)
+class GroupRMSNormSpec:
+    """RMS norm in groups: the ``dim`` coordinates are split into ``groups`` equal consecutive parts, each part is
+    divided by its own sqrt(mean(part^2) + eps), and the whole is multiplied by a weight of size ``dim``. ``tensor``:
+    the weight's name under the part's prefix (empty: the prefix itself names it)."""
+    dim: int
+    eps: float
+    groups: int = 1
+    tensor: str = ""
+
+
+@dataclass(frozen=True)
 class SinusoidSpec:
     """Absolute position vector added to the embedding: entry 2i = sin(p * base^(-2i/dim)), entry
     2i+1 = cos of the same angle."""
@@ -106,7 +117,10 @@ class MaskedAttentionSpec:
     v <- (1 - lam) v + lam v_source with its learned number ``vmix`` (both kinds hold the tensor; the source's is unused).
     ``values_in_keys``: a token's value row is the first ``v_head_dim`` numbers of its key row (the rows of latents of an
     attention through latents): the cache keeps the key rows alone and every kernel reads values from them (the tcgen05 prompt
-    kernel and the split single-token kernel, which want a store of values, are not used then)."""
+    kernel and the split single-token kernel, which want a store of values, are not used then).
+    ``bias``: q, k and v have biases (tensors ``q.b``, ``k.b``, ``v.b``), added in the projection. ``q_temp`` = (coef,
+    every): q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1). ``talk``: the heads' scores are
+    mixed before the masks and the softmax, score_h <- sum_g T[h, g] score_g with the tensor ``talk`` [heads, heads]."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -127,6 +141,60 @@ class MaskedAttentionSpec:
     norm_after_rotation: bool = False
     value_mix: Optional[str] = None
     values_in_keys: bool = False
+    bias: bool = False
+    q_temp: Optional[Tuple[float, int]] = None
+    talk: bool = False
+
+
+@dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Differential attention: every head has two softmax maps over the same values. q has heads * 2 * head_dim rows and
+    k kv_heads * 2 * head_dim, head by head as [map 1 | map 2]; q, k, v have biases (``q.b`` ..); no rotation; q at
+    position p times 1 + coef * ln(floor((p + 1) / every) + 1) with ``q_temp`` = (coef, every); each map is a causal
+    softmax of (q . k) * scale (inside ``window`` if given). With a1, a2 the maps' outputs and lambda = exp(lq1 . lk1) -
+    exp(lq2 . lk2) + diff (tensors of size head_dim), a head's output is unit_rms(a1 - lambda a2) * (1 - diff), the root
+    mean square over its v_head_dim values with ``norm_eps`` inside the root; then the output projection ``o``."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    diff: float
+    norm_eps: float
+    q_temp: Optional[Tuple[float, int]] = None
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class LowerBoundRecurrenceSpec:
+    """HGRN2: linear attention whose forget gate also decides what is written. q = silu(W_q x) (heads x head_dim), v =
+    W_v x (heads x v_head_dim), f = l + (1 - l) sigmoid(W_f x + b) per head and channel with the lower bound l = ``lower``;
+    per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T (state [head_dim, v_head_dim], float32, zero at the start), o_t =
+    S_t^T q_t; each head's o through an RMS norm over v_head_dim with the weight ``norm`` shared by the heads; then ``o``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    norm_eps: float
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """Mamba-2 (state-space duality). inner = heads * v_head_dim, N = state_dim, G = groups. ``in`` x is laid out as
+    [z: inner | x: inner | B: G N | C: G N | dt: heads]; x, B, C pass a causal convolution per channel (``conv`` [channels,
+    taps], last column the current token's, bias ``conv.b``) and SiLU; dt <- softplus(dt + dt_bias); per head (head h
+    reads group h / (heads / G)) S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T (state [N, v_head_dim], float32), y_t =
+    S_t^T C_t + D_h x_t; y * silu(z), an RMS norm in ``norm_groups`` equal parts times ``norm``, then ``o``. The last
+    taps - 1 inputs of the convolution are per-sequence state too."""
+    hidden_size: int
+    num_heads: int
+    v_head_dim: int
+    state_dim: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
 
 
 @dataclass(frozen=True)
@@ -216,7 +284,12 @@ class RoutedMLPSpec:
     s + ``correction`` (a tensor), among the experts of the ``keep_groups`` best of ``groups`` equal groups of
     neighbours (group score: the sum of its two largest choice scores), the ``top`` largest; the weights are the
     chosen s over their sum (+ 1e-20), times ``route_scale``. ``shared_ff``: a shared expert of that inner size
-    (``shared.gate/up/down``) runs for every token, times sigmoid(w_sg . x) (``shared.sg`` [1, hidden])."""
+    (``shared.gate/up/down``) runs for every token, times sigmoid(w_sg . x) (``shared.sg`` [1, hidden]).
+    Options: ``correction`` False: no such tensor, the choice goes by s; ``renorm`` False: the weights are the chosen s
+    themselves (times ``route_scale``); ``weight_on_input``: the weight multiplies the expert's input, out = sum
+    expert(w x), not its output; ``shared_gate`` False: the shared expert is added as it is. ``activation`` "clamped":
+    with g = min(gate x, limit), u = clamp(up x, -limit, limit) an expert is down(g sigmoid(1.702 g) (u + 1)), with
+    ``limit`` for the routed experts and ``shared_limit`` for the shared one."""
     hidden_size: int
     expert_ff: int
     num_experts: int
@@ -226,6 +299,12 @@ class RoutedMLPSpec:
     route_scale: float = 1.0
     shared_ff: Optional[int] = None
     activation: str = "silu"
+    correction: bool = True
+    renorm: bool = True
+    weight_on_input: bool = False
+    shared_gate: bool = True
+    limit: Optional[float] = None
+    shared_limit: Optional[float] = None
 
 
 @dataclass(frozen=True)

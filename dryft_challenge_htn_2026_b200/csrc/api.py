@@ -1076,16 +1076,18 @@ def cast_rows(h, a_out):
     _check(lib, lib.dk_cast_rows(_dt(a_out), _p(h), _p(a_out), c_longlong(h.numel()), _stream()), "cast_rows")
 
 
-ACT_SILU, ACT_GELU_TANH = 0, 1
+ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED = 0, 1, 2
 
 
-def act_mul(gu, out, act):
-    """out[r, c] = act(gu[r, c]) * gu[r, I + c] for gu [rows, 2I]; act ACT_SILU or ACT_GELU_TANH."""
+def act_mul(gu, out, act, limit=0.0):
+    """out[r, c] = act(gu[r, c]) * gu[r, I + c] for gu [rows, 2I]; act ACT_SILU or ACT_GELU_TANH, or ACT_CLAMPED with
+    ``limit``: g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' sigmoid(1.702 g') (u' + 1)."""
     _need(gu, "gu", None, 2), _need(out, "out", gu.dtype, 2)
     if gu.shape != (out.shape[0], 2 * out.shape[1]):
         raise KernelError("act_mul: shapes do not match")
     lib = _lib("elementwise.cu")
-    _check(lib, lib.dk_act_mul(_dt(gu), _p(gu), _p(out), c_longlong(gu.shape[0]), out.shape[1], int(act), _stream()), "act_mul")
+    _check(lib, lib.dk_act_mul(_dt(gu), _p(gu), _p(out), c_longlong(gu.shape[0]), out.shape[1], int(act), c_float(limit),
+                               _stream()), "act_mul")
 
 
 # ------------------------------------------- short convolution, head norm and rotation before a cache
@@ -1097,7 +1099,7 @@ NORM_NONE, NORM_BEFORE_ROTATION, NORM_AFTER_ROTATION = 0, 1, 2
 
 def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos, sin, rot_dims, row_pos, row_seq, seq_pos0,
                    seq_slot, n_heads, n_kv_heads, head_dim, v_head_dim, k_store=None, v_store=None, page_table=None,
-                   norm_mode=None, v_mix=None, v_src=None):
+                   norm_mode=None, v_mix=None, v_src=None, bias=None, q_temp=None, q_split=1):
     """Rows [q | k | v] of a fused projection -> ``out`` rows of the same layout: a causal convolution of
     ``taps`` taps over time on every channel (``w_conv`` [channels, taps]; earlier rows of the same step, or
     the sequence's ``state`` [slots, taps-1, channels] for positions before it), then per q and k head an RMS
@@ -1106,9 +1108,16 @@ def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos,
     default the norm runs before the rotation when weights are given; ``NORM_AFTER_ROTATION`` puts it behind, and with
     either mode and no weights the heads are divided by their root mean square alone. ``v_src`` (rows of v heads, the
     projection's type) with ``v_mix`` (float32, one number): v <- (1 - v_mix) v + v_mix v_src. The state is
-    only read: ``conv_state_update`` moves it on afterwards. With ``k_store`` / ``v_store`` [pages, nkv, PAGE, size] and
+    only read: ``conv_state_update`` moves it on afterwards. ``bias`` (float32 [channels]) is added to the projection
+    before the norm; ``q_temp`` = (coef, every) multiplies every q head by 1 + coef * ln(floor((p + 1) / every) + 1) at
+    position p, last of all; ``q_split`` = s makes s query heads of each query head (part i of the head at its place in
+    head i, zeros elsewhere), so ``out`` is (s - 1) * n_heads * head_dim wider than ``proj``. With ``k_store`` / ``v_store`` [pages, nkv, PAGE, size] and
     ``page_table`` the k and v heads also go to each token's place in the paged cache."""
     _need_rows(proj, "proj"), _need_rows(out, "out", proj.dtype), _need_rows(v_src, "v_src", proj.dtype)
+    _need(bias, "bias", torch.float32, 1)
+    q_split = int(q_split)
+    if q_split < 1 or head_dim % q_split or (q_temp is not None and int(q_temp[1]) < 1):
+        raise KernelError(f"conv_norm_rope: q_split {q_split} of heads of {head_dim}, q_temp {q_temp}")
     if norm_mode is None:
         norm_mode = NORM_BEFORE_ROTATION if q_norm_w is not None else NORM_NONE
     if (v_src is None) != (v_mix is None) or (v_src is not None and (v_src.shape != (proj.shape[0], n_kv_heads * v_head_dim)
@@ -1120,7 +1129,8 @@ def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos,
     _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
     for t, n in ((row_pos, "row_pos"), (row_seq, "row_seq"), (seq_pos0, "seq_pos0"), (seq_slot, "seq_slot")):
         _need(t, n, torch.int32, 1)
-    if proj.shape[1] != C or out.shape != proj.shape or not 1 <= taps <= SHORT_CONV_MAX_TAPS or \
+    if proj.shape[1] != C or out.shape != (proj.shape[0], C + (q_split - 1) * n_heads * head_dim) or \
+            (bias is not None and bias.numel() != C) or not 1 <= taps <= SHORT_CONV_MAX_TAPS or \
             (taps > 1 and (state is None or w_conv is None or tuple(state.shape[1:]) != (taps - 1, C) or tuple(w_conv.shape) != (C, taps))) or \
             rot_dims % 2 or rot_dims > head_dim or (rot_dims and (cos is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape)) or \
             max(head_dim, v_head_dim) > 256 or (q_norm_w is not None and q_norm_w.numel() != head_dim) or \
@@ -1137,7 +1147,9 @@ def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos,
                                       c_float(eps), _p(v_mix), _p(v_src), c_longlong(v_src.stride(0) if v_src is not None else 0), _p(cos),
                                       _p(sin), int(rot_dims), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot),
                                       proj.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, _p(k_store), _p(v_store),
-                                      _p(page_table), page_table.shape[1] if page_table is not None else 0, _stream()),
+                                      _p(page_table), page_table.shape[1] if page_table is not None else 0, _p(bias),
+                                      c_float(q_temp[0] if q_temp is not None else 0.0),
+                                      int(q_temp[1]) if q_temp is not None else 0, q_split, _stream()),
            "conv_norm_rope")
 
 
@@ -1214,11 +1226,13 @@ def latent_value(o_lat, w_uv, out, n_heads, kv_rank, vdim):
 MOE_MAX_EXPERTS = 256
 
 
-def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, idx, wt, shared_gate, scores=None):
+def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, idx, wt, shared_gate, scores=None,
+              renorm=True):
     """Router of a mixture of experts, float32 arithmetic: s = sigmoid(w_router x); the ``top`` experts with the
     largest s + correction among the ``keep`` best of ``groups`` groups of neighbours (group score: its two
     largest s + correction) -> ``idx`` int32 [T, top]; ``wt`` float32 [T, top] = their s over the sum, times
-    ``scale``; ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given. Two kernels: the
+    ``scale`` (``renorm`` False: the chosen s themselves, times ``scale``; ``correction`` None: the choice goes by s);
+    ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given. Two kernels: the
     scores (``scores`` float32 [T, E], scratch), then the choice."""
     _need(x, "x", None, 2), _need(w_router, "w_router", torch.float32, 2), _need(correction, "correction", torch.float32, 1)
     _need(w_shared_gate, "w_shared_gate", torch.float32, 1), _need(idx, "idx", torch.int32, 2), _need(wt, "wt", torch.float32, 2)
@@ -1236,20 +1250,25 @@ def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, 
         raise KernelError("moe_route: scores must be float32 [tokens, experts]")
     lib = _lib("moe.cu")
     _check(lib, lib.dk_moe_route(_dt(x), _p(x), W, _p(w_router), _p(correction), _p(w_shared_gate), E, int(top), int(groups),
-                                 int(keep), c_float(scale), _p(idx), _p(wt), _p(shared_gate), _p(scores), T, _stream()),
+                                 int(keep), c_float(scale), _p(idx), _p(wt), _p(shared_gate), _p(scores), T, int(bool(renorm)),
+                                 _stream()),
            "moe_route", 2)
 
 
-def moe_up_rows(x, w_gate_up, idx, mid, act=0):
+def moe_up_rows(x, w_gate_up, idx, mid, act=0, in_wt=None, limit=0.0):
     """mid[t * top + j] = act(gate_e x_t) * (up_e x_t) for e = idx[t, j]; w_gate_up [E, 2 ff, W] with an expert's
-    gate rows before its up rows. A warp per output, float32 sums."""
+    gate rows before its up rows. A warp per output, float32 sums. ``in_wt`` float32 [T, top]: the pair's weight on the
+    expert's input (both sums times it before the activation). ``act`` ACT_CLAMPED with ``limit``: g' = min(g, limit),
+    u' = clamp(u, -limit, limit), out = g' sigmoid(1.702 g') (u' + 1)."""
+    _need(in_wt, "in_wt", torch.float32, 2)
     _need(x, "x", None, 2), _need(w_gate_up, "w_gate_up", x.dtype, 3), _need(idx, "idx", torch.int32, 2), _need(mid, "mid", x.dtype, 2)
     T, W = x.shape
     top, ff = idx.shape[1], mid.shape[1]
     if w_gate_up.shape[1:] != (2 * ff, W) or mid.shape[0] != T * top or idx.shape[0] != T:
         raise KernelError("moe_up_rows: shapes do not match")
     lib = _lib("moe.cu")
-    _check(lib, lib.dk_moe_up_rows(_dt(x), _p(x), W, _p(w_gate_up), _p(idx), _p(mid), ff, top, T, int(act), _stream()), "moe_up_rows")
+    _check(lib, lib.dk_moe_up_rows(_dt(x), _p(x), W, _p(w_gate_up), _p(idx), _p(mid), ff, top, T, int(act), _p(in_wt),
+                                   c_float(limit), _stream()), "moe_up_rows")
 
 
 def moe_down_rows(mid, w_down, idx, wt, shared, shared_gate, out):
@@ -1260,7 +1279,7 @@ def moe_down_rows(mid, w_down, idx, wt, shared, shared_gate, out):
     _need(out, "out", mid.dtype, 2)
     T, top = idx.shape
     W, ff = w_down.shape[1:]
-    if mid.shape != (T * top, ff) or out.shape != (T, W) or wt.shape != (T, top) or (shared is not None and shared.shape != (T, W)):
+    if mid.shape != (T * top, ff) or out.shape != (T, W) or (wt is not None and wt.shape != (T, top)) or (shared is not None and shared.shape != (T, W)):
         raise KernelError("moe_down_rows: shapes do not match")
     lib = _lib("moe.cu")
     _check(lib, lib.dk_moe_down_rows(_dt(mid), _p(mid), _p(w_down), _p(idx), _p(wt), _p(shared), _p(shared_gate), _p(out), W, ff,
@@ -1276,17 +1295,20 @@ def moe_tiles_take(x, expert_ff):
     return x.dtype == torch.bfloat16 and x.shape[0] > 32 and x.shape[1] % 32 == 0 and expert_ff % 32 == 0
 
 
-def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, act=0, scratch=None):
+def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, act=0, scratch=None, in_wt=None, limit=0.0):
     """The routed experts for many tokens: pairs sorted by expert on the device, tiles of 64 pairs as matrix
     products on mma.sync tensor cores (gate/up with the activation, then down), then the weighted sum per token
-    plus shared_gate * shared. ``scratch(key, make)``: where buffers that outlive the call may be kept."""
+    plus shared_gate * shared. ``scratch(key, make)``: where buffers that outlive the call may be kept. ``wt`` None: the
+    plain sum; ``in_wt``, ``limit``: as in ``moe_up_rows``."""
+    _need(in_wt, "in_wt", torch.float32, 2)
     _need(x, "x", torch.bfloat16, 2), _need(w_gate_up, "w_gate_up", torch.bfloat16, 3), _need(w_down, "w_down", torch.bfloat16, 3)
     _need(idx, "idx", torch.int32, 2), _need(wt, "wt", torch.float32, 2), _need(shared, "shared", torch.bfloat16, 2)
     _need(shared_gate, "shared_gate", torch.float32, 1), _need(out, "out", torch.bfloat16, 2)
     T, W = x.shape
     top = idx.shape[1]
     E, ff = w_down.shape[0], w_down.shape[2]
-    if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape[1] != W or idx.shape[0] != T or wt.shape != idx.shape or \
+    if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape[1] != W or idx.shape[0] != T or \
+            any(w is not None and w.shape != idx.shape for w in (wt, in_wt)) or \
             out.shape != (T, W) or W % 32 or ff % 32 or E > MOE_MAX_EXPERTS or (shared is not None and shared.shape != (T, W)):
         raise KernelError("moe_experts_tiles: shapes do not match (inner sizes in steps of 32)")
     P = T * top
@@ -1300,8 +1322,8 @@ def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, a
     perm, inv, tiles, mid, y = scratch(("moe_tiles", T, top, E, ff, W), make) if scratch is not None else make()
     lib = _lib("moe_tiles.cu")
     _check(lib, lib.dk_moe_sort(_p(idx), P, E, _p(perm), _p(inv), _p(tiles), max_tiles, _stream()), "moe_sort")
-    _check(lib, lib.dk_moe_up_tiles(_p(x), _p(w_gate_up), _p(tiles), max_tiles, _p(perm), top, _p(mid), ff, W, int(act), _stream()),
-           "moe_up_tiles")
+    _check(lib, lib.dk_moe_up_tiles(_p(x), _p(w_gate_up), _p(tiles), max_tiles, _p(perm), top, _p(mid), ff, W, int(act), _p(in_wt),
+                                    c_float(limit), _stream()), "moe_up_tiles")
     _check(lib, lib.dk_moe_down_tiles(_p(mid), _p(w_down), _p(tiles), max_tiles, _p(y), W, ff, _stream()), "moe_down_tiles")
     _check(lib, lib.dk_moe_sum(_p(y), _p(inv), _p(wt), _p(shared), _p(shared_gate), _p(out), T, W, top, _stream()), "moe_sum")
 
@@ -1334,3 +1356,137 @@ def gated_linear_attention(q, k, v, out, state, cu_q, seq_pos0, seq_slot, z, z_b
                                                    c_float(1.0 / tau), c_longlong(q.shape[0]), _p(out), _p(state), _p(cu_q),
                                                    _p(seq_pos0), _p(seq_slot), c_float(q_scale), n_seq, n_heads, head_dim,
                                                    v_head_dim, _stream()), "gated_linear_attention", 2)
+
+
+# ----------------------------------------------------------------- norms over parts of a row, and what ends in one
+def add_group_rmsnorm(h, delta, norm_w, eps, groups, a_out, rows=None):
+    """h += delta (a tensor, a ``Partial`` or None); a_out = norm_w * (each of ``groups`` equal consecutive parts of
+    the row over its own root mean square, eps inside the root). With ``rows`` (int32 indices) only those rows, into
+    a_out[0..len(rows)), and h is left as it is."""
+    delta, parts, n_parts, stride = _parts(delta)
+    _need(h, "h", torch.float32, 2), _need(delta, "delta", a_out.dtype, 2), _need(norm_w, "norm_w", torch.float32, 1)
+    _need(rows, "rows", torch.int32, 1), _need(a_out, "a_out", None, 2)
+    H = h.shape[1]
+    if groups < 1 or H % groups or norm_w.numel() != H or (delta is not None and delta.shape != h.shape):
+        raise KernelError(f"add_group_rmsnorm: {groups} parts of rows of {H}, or shapes that do not match")
+    n = h.shape[0] if rows is None else rows.numel()
+    lib = _lib("group_norm.cu")
+    _check(lib, lib.dk_add_group_rmsnorm(_dt(a_out), _p(h), _p(delta), parts, n_parts, stride, _p(rows), _p(norm_w),
+                                         c_float(eps), n, H, int(groups), _p(a_out), _stream()), "add_group_rmsnorm")
+
+
+def gate_group_norm(o, x, skip, z, weight, eps, groups, out_scale, out):
+    """out = weight * grouped_rmsnorm((o + skip_h * x) * silu(z)) * out_scale: o and x float32 [T, n] with n = heads *
+    value size, ``skip`` float32 [heads] (None: no such term), the gate rows ``z`` and ``out`` in the storage type (rows
+    of wider matrices), the norm over each of ``groups`` equal parts of the row."""
+    _need(o, "o", torch.float32, 2), _need(x, "x", torch.float32, 2), _need(skip, "skip", torch.float32, 1)
+    _need(weight, "weight", torch.float32, 1), _need_rows(z, "z", out.dtype), _need_rows(out, "out")
+    T, n = o.shape
+    heads = skip.numel() if skip is not None else 1
+    if x.shape != o.shape or z.shape != o.shape or out.shape != o.shape or weight.numel() != n or groups < 1 or n % groups \
+            or n % heads:
+        raise KernelError("gate_group_norm: shapes do not match")
+    lib = _lib("group_norm.cu")
+    _check(lib, lib.dk_gate_group_norm(_dt(out), _p(o), _p(x), _p(skip), n // heads, _p(z), c_longlong(z.stride(0)), _p(weight),
+                                       c_float(eps), c_float(out_scale), _p(out), c_longlong(out.stride(0)), T, n, int(groups),
+                                       _stream()), "gate_group_norm")
+
+
+def diff_combine(a, lam, eps, out_scale, out, n_heads, v_head_dim):
+    """``a`` [T, 2 * n_heads * v_head_dim]: head 2h holds the first map's output of head h, head 2h + 1 the second's.
+    out[t, h] = unit_rms(a1 - lam * a2) * out_scale per head (eps inside the root, no weight)."""
+    _need_rows(a, "a"), _need_rows(out, "out", a.dtype)
+    if a.shape[1] != 2 * n_heads * v_head_dim or out.shape != (a.shape[0], n_heads * v_head_dim) or v_head_dim > 256:
+        raise KernelError("diff_combine: shapes do not match (value heads up to 256)")
+    lib = _lib("group_norm.cu")
+    _check(lib, lib.dk_diff_combine(_dt(a), _p(a), c_longlong(a.stride(0)), c_float(lam), c_float(eps), c_float(out_scale),
+                                    _p(out), c_longlong(out.stride(0)), a.shape[0], n_heads, v_head_dim, _stream()), "diff_combine")
+
+
+# ------------------------------------------------------------- recurrences over a float32 state, and what feeds them
+def hgrn2_prepare(proj, f_bias, lower, q32, k32, a32, v32):
+    """Rows [q | f | v] of a projection (n, n and nv wide) -> float32 q32 = silu(q), a32 = l + (1 - l) sigmoid(f + b),
+    k32 = 1 - a32, v32 = v."""
+    _need_rows(proj, "proj"), _need(f_bias, "f_bias", torch.float32, 1), _need(lower, "lower", torch.float32, 1)
+    for t, nm in ((q32, "q32"), (k32, "k32"), (a32, "a32"), (v32, "v32")):
+        _need(t, nm, torch.float32, 2)
+    T, n, nv = proj.shape[0], q32.shape[1], v32.shape[1]
+    if proj.shape[1] != 2 * n + nv or f_bias.numel() != n or lower.numel() != n or k32.shape != (T, n) or a32.shape != (T, n) or \
+            q32.shape[0] != T or v32.shape[0] != T:
+        raise KernelError("hgrn2_prepare: shapes do not match")
+    lib = _lib("recurrence.cu")
+    _check(lib, lib.dk_hgrn2_prepare(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(f_bias), _p(lower), _p(q32), _p(k32),
+                                     _p(a32), _p(v32), T, n, nv, _stream()), "hgrn2_prepare")
+
+
+def ssd_prepare(xbc, dt, state, w_conv, conv_bias, taps, dt_bias, a_log, row_pos, row_seq, seq_pos0, seq_slot, x32, b32, c32,
+                dt32, a32):
+    """``xbc`` [T, C] and ``dt`` [T, heads]: columns of one projection (one row stride). [x32 | b32 | c32] = silu(conv(xbc) + bias)
+    with ``w_conv`` [C, taps] whose last column is the current token's and the sequence's ``state`` [slots, taps - 1, C]
+    for positions before the step (read only: ``conv_state_update`` moves it on); dt32 = softplus(dt + dt_bias);
+    a32 = exp(-exp(a_log) * dt32)."""
+    _need_rows(xbc, "xbc"), _need_rows(dt, "dt", xbc.dtype), _need(state, "state", xbc.dtype, 3), _need(w_conv, "w_conv", xbc.dtype, 2)
+    _need(conv_bias, "conv_bias", torch.float32, 1), _need(dt_bias, "dt_bias", torch.float32, 1), _need(a_log, "a_log", torch.float32, 1)
+    for t, nm in ((row_pos, "row_pos"), (row_seq, "row_seq"), (seq_pos0, "seq_pos0"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32, 1)
+    for t, nm in ((x32, "x32"), (b32, "b32"), (c32, "c32"), (dt32, "dt32"), (a32, "a32")):
+        _need(t, nm, torch.float32, 2)
+    T, C = xbc.shape
+    nh = dt.shape[1]
+    inner, nbc = x32.shape[1], b32.shape[1]
+    if xbc.stride(0) != dt.stride(0) or tuple(w_conv.shape) != (C, taps) or not 1 <= taps <= SHORT_CONV_MAX_TAPS or \
+            (taps > 1 and (state is None or tuple(state.shape[1:]) != (taps - 1, C))) or dt_bias.numel() != nh or a_log.numel() != nh or \
+            inner + 2 * nbc != C or x32.shape[0] != T or b32.shape != (T, nbc) or c32.shape != (T, nbc) or dt32.shape != (T, nh) or a32.shape != (T, nh) or (conv_bias is not None and conv_bias.numel() != C):
+        raise KernelError("ssd_prepare: shapes do not match")
+    lib = _lib("recurrence.cu")
+    _check(lib, lib.dk_ssd_prepare(_dt(xbc), _p(xbc), _p(dt), c_longlong(xbc.stride(0)), _p(state), _p(w_conv), _p(conv_bias), int(taps),
+                                   _p(dt_bias), _p(a_log), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot), _p(x32), _p(b32), _p(c32), _p(dt32),
+                                   _p(a32), T, inner, nbc, nh, _stream()), "ssd_prepare")
+
+
+def recurrence(q, k, k_factor, decay, v, out, state, cu_q, seq_pos0, seq_slot, n_seq, n_heads, head_dim, v_head_dim):
+    """S <- diag(decay_t) S + (k_factor_t k_t) v_t^T, o_t = S^T q_t per (sequence, head), token by token, all float32:
+    q, k [T, groups * head_dim] (head h reads group h / (n_heads / groups)), ``k_factor`` [T, n_heads] or None, ``decay``
+    [T, n_heads * head_dim] (per key channel) or [T, n_heads] (one number a head), v and out [T, n_heads * v_head_dim],
+    state [slots, n_heads, head_dim, v_head_dim]. Rows of sequence s are cu_q[s] .. cu_q[s + 1] (``cu_q`` None: row s
+    alone); seq_pos0[s] < 0 marks a padding row."""
+    for t, nm in ((q, "q"), (k, "k"), (k_factor, "k_factor"), (decay, "decay"), (v, "v"), (out, "out")):
+        _need(t, nm, torch.float32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
+    T = q.shape[0]
+    if q.shape[1] % head_dim or k.shape != q.shape:
+        raise KernelError("recurrence: q and k must be [tokens, groups * head_dim]")
+    groups = q.shape[1] // head_dim
+    per_head = decay.shape[1] == n_heads and head_dim != 1
+    if groups < 1 or n_heads % groups or decay.shape not in ((T, n_heads), (T, n_heads * head_dim)) or \
+            v.shape != (T, n_heads * v_head_dim) or out.shape != v.shape or head_dim > 256 or \
+            tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or (k_factor is not None and k_factor.shape != (T, n_heads)):
+        raise KernelError("recurrence: shapes do not match (key sizes up to 256)")
+    lib = _lib("recurrence.cu")
+    _check(lib, lib.dk_recurrence(_p(q), _p(k), groups, _p(k_factor), _p(decay), int(per_head), _p(v), _p(out), _p(state), _p(cu_q),
+                                  _p(seq_pos0), _p(seq_slot), n_seq, n_heads, head_dim, v_head_dim, _stream()), "recurrence")
+
+
+# ------------------------------------------------------------------ attention whose heads' scores are mixed
+TALK_MAX_HEADS = 64
+TALK_MAX_OUT = 16 * 256     # n_heads * v_head_dim a block of attention_talk holds
+
+
+def attention_talk(q, out, out_scale, k_store, v_store, row_pos, row_seq, page_table, n_heads, n_kv_heads, head_dim, v_head_dim,
+                   window, scale, talk):
+    """Float32-arithmetic attention of every token row over its sequence's cached keys in which the heads' scores are
+    mixed before the softmax: s'_h = sum_g talk[h, g] (q_g . k) * scale; causal, inside ``window`` (0 or None: none);
+    out = heads * out_scale. q and out may be rows of wider matrices. Any phase; float32 or bfloat16 storage."""
+    _need_rows(q, "q"), _need_rows(out, "out", q.dtype), _need(talk, "talk", torch.float32, 2)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", q.dtype), _need(v_store, "v_store", q.dtype)
+    if n_heads > TALK_MAX_HEADS or n_heads % n_kv_heads or n_heads * v_head_dim > TALK_MAX_OUT or tuple(talk.shape) != (n_heads, n_heads) \
+            or q.shape[1] != n_heads * head_dim or out.shape != (q.shape[0], n_heads * v_head_dim):
+        raise KernelError(f"attention_talk: {n_heads}:{n_kv_heads} heads of {head_dim}/{v_head_dim} (up to {TALK_MAX_HEADS} heads, "
+                          f"heads x value size up to {TALK_MAX_OUT})")
+    lib = _lib("attention_talk.cu")
+    _check(lib, lib.dk_attention_talk(_dt(q), _p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), c_float(out_scale),
+                                      _p(k_store), _p(v_store), _p(row_pos), _p(row_seq), _p(page_table), page_table.shape[1],
+                                      q.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, int(window or 0), c_float(scale),
+                                      _p(talk), _stream()), "attention_talk")

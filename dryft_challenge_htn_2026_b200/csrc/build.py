@@ -126,6 +126,7 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
             ("gemm_tc.cu", None), ("sampling.cu", None),
             ("sample_noalloc.cu", None), ("attention_masked.cu", None), ("linear_attention.cu", None),
             ("short_conv.cu", None), ("moe.cu", None), ("moe_tiles.cu", None), ("latent.cu", None),
+            ("group_norm.cu", None), ("recurrence.cu", None), ("attention_talk.cu", None),
             ("attention_shared_rows.cu", {"HD": 576, "HDV": 512})]
     jobs += [("attention_bf16.cu", {"HD": hd}) for hd in head_dims]
     jobs += [("attention_tc.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]

@@ -924,24 +924,31 @@ DK_EXPORT int dk_cast_rows(int dtype, const float* h, void* a, long long n, cuda
 }
 
 // out[r, c] = act(gu[r, c]) * gu[r, I + c] for rows [gate | up]; act 0: SiLU, 1: the tanh form of GELU,
-// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))). Arithmetic in float32.
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: with g' = min(g, limit) and u' = clamp(u, -limit, limit),
+// g' sigmoid(1.702 g') (u' + 1). Arithmetic in float32.
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 template <typename T>
-__global__ void act_mul_kernel(const T* gu, T* out, size_t n, int I, int act) {
+__global__ void act_mul_kernel(const T* gu, T* out, size_t n, int I, int act, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     size_t r = idx / I, c = idx % I;
-    const float g = to_f(gu[r * 2 * I + c]);
-    const float u = to_f(gu[r * 2 * I + I + c]);
+    float g = to_f(gu[r * 2 * I + c]);
+    float u = to_f(gu[r * 2 * I + I + c]);
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        out[idx] = from_f<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+        return;
+    }
     out[idx] = from_f<T>((act == 1 ? gelu_tanh_f(g) : g / (1.f + expf(-g))) * u);
 }
 
-DK_EXPORT int dk_act_mul(int dtype, const void* gu, void* out, long long n_rows, int I, int act, cudaStream_t st) {
+DK_EXPORT int dk_act_mul(int dtype, const void* gu, void* out, long long n_rows, int I, int act, float limit, cudaStream_t st) {
     size_t n = (size_t)n_rows * I;
     DISPATCH_T(dtype, return dk_launch(act_mul_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
-                                       (const T*)gu, (T*)out, n, I, act));
+                                       (const T*)gu, (T*)out, n, I, act, limit));
 }

@@ -97,7 +97,7 @@ moe_scores_kernel(const T* x, int W, const float* __restrict__ wr, const float* 
 // Choice: a warp a token, from the token's scores.
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_choose_kernel(const float* scores, const float* __restrict__ corr, int E, int top, int groups, int keep, float scale,
-                  int* idx, float* wt, int n_tok) {
+                  int* idx, float* wt, int n_tok, int renorm) {
     extern __shared__ __align__(16) unsigned char route_smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -154,13 +154,19 @@ moe_choose_kernel(const float* scores, const float* __restrict__ corr, int E, in
     }
     if (lane < top) {
         const int e = idx[(size_t)t * top + lane];
-        wt[(size_t)t * top + lane] = s[e] / (wsum + 1e-20f) * scale;
+        wt[(size_t)t * top + lane] = (renorm ? s[e] / (wsum + 1e-20f) : s[e]) * scale;    // the scores as they are, or over their sum
     }
 }
 
-__device__ __forceinline__ float moe_act(float z, int act) {
-    if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    return z / (1.f + expf(-z));
+// act 0: silu(g) u; 1: gelu_tanh(g) u; 2: with g' = min(g, limit) and u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
+__device__ __forceinline__ float moe_gated(float g, float u, int act, float limit) {
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+    }
+    if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return g / (1.f + expf(-g)) * u;
 }
 
 // 16 bytes of a row as floats: 8 bfloat16 or 4 float32 values
@@ -191,7 +197,7 @@ template <> struct Vec<float> {
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(128)
 moe_up_rows_kernel(const T* x, int W, const T* __restrict__ wgu, const int* idx, T* mid, int ff, int top, int rows_per_block,
-                   int act) {
+                   int act, const float* in_wt, float limit) {
     extern __shared__ float xs[];
     pdl_wait();
     pdl_launch_dependents();
@@ -229,7 +235,11 @@ moe_up_rows_kernel(const T* x, int W, const T* __restrict__ wgu, const int* idx,
         }
         ag = warp_sum(ag);
         au = warp_sum(au);
-        if (lane == 0) mid[(size_t)pair * ff + f] = from_f<T>(moe_act(ag, act) * au);
+        if (in_wt != nullptr) {      // the pair's weight on the expert's input: W (w x) = w (W x)
+            ag *= in_wt[pair];
+            au *= in_wt[pair];
+        }
+        if (lane == 0) mid[(size_t)pair * ff + f] = from_f<T>(moe_gated(ag, au, act, limit));
     }
 }
 
@@ -243,7 +253,7 @@ moe_down_rows_kernel(const T* mid, const T* __restrict__ wd, const int* idx, con
     pdl_launch_dependents();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x)
-        ms[i] = to_f(mid[(size_t)t * top * ff + i]) * wt[(size_t)t * top + i / ff];
+        ms[i] = to_f(mid[(size_t)t * top * ff + i]) * (wt != nullptr ? wt[(size_t)t * top + i / ff] : 1.f);
     __syncthreads();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int c_end = min(W, (int)(blockIdx.y + 1) * rows_per_block);
@@ -290,7 +300,7 @@ static int launch_scores(const void* x, int W, const float* wr, const float* wsg
 // scores: float32 scratch [n_tok, E]
 DK_EXPORT int dk_moe_route(int dtype, const void* x, int W, const float* wr, const float* corr, const float* wsg, int E,
                            int top, int groups, int keep, float scale, int* idx, float* wt, float* sgate, float* scores, int n_tok,
-                           cudaStream_t st) {
+                           int renorm, cudaStream_t st) {
     if (E < 1 || E > MOE_MAX_EXPERTS || top < 1 || top > 32 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups ||
         scores == nullptr || (sizeof(float) * ROUTE_TOKENS * W > 200 * 1024))
         return (int)cudaErrorInvalidValue;
@@ -299,18 +309,19 @@ DK_EXPORT int dk_moe_route(int dtype, const void* x, int W, const float* wr, con
     if (e) return e;
     const size_t smem = sizeof(float) * 3 * (size_t)E * ROUTE_WARPS;
     return dk_launch(moe_choose_kernel, dim3((n_tok + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(32 * ROUTE_WARPS), smem, st, scores, corr,
-                     E, top, groups, keep, scale, idx, wt, n_tok);
+                     E, top, groups, keep, scale, idx, wt, n_tok, renorm);
 }
 
 template <typename T, bool VEC>
 static int launch_up(const void* x, int W, const void* wgu, const int* idx, void* mid, int ff, int top, int n_tok, int act,
-                     cudaStream_t st) {
+                     const float* in_wt, float limit, cudaStream_t st) {
     const int rpb = 16;
     const dim3 grid(n_tok * top, (ff + rpb - 1) / rpb), block(128);
     const size_t smem = sizeof(float) * (size_t)W;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_rows_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return dk_launch(moe_up_rows_kernel<T, VEC>, grid, block, smem, st, (const T*)x, W, (const T*)wgu, idx, (T*)mid, ff, top, rpb, act);
+    return dk_launch(moe_up_rows_kernel<T, VEC>, grid, block, smem, st, (const T*)x, W, (const T*)wgu, idx, (T*)mid, ff, top, rpb, act,
+                     in_wt, limit);
 }
 
 template <typename T, bool VEC>
@@ -326,13 +337,13 @@ static int launch_down(const void* mid, const void* wd, const int* idx, const fl
 }
 
 DK_EXPORT int dk_moe_up_rows(int dtype, const void* x, int W, const void* wgu, const int* idx, void* mid, int ff, int top,
-                             int n_tok, int act, cudaStream_t st) {
+                             int n_tok, int act, const float* in_wt, float limit, cudaStream_t st) {
     const bool vec = (uintptr_t)wgu % 16 == 0 && W % (dtype == 0 ? 4 : 8) == 0;
     if (dtype == 0)
-        return vec ? launch_up<float, true>(x, W, wgu, idx, mid, ff, top, n_tok, act, st)
-                   : launch_up<float, false>(x, W, wgu, idx, mid, ff, top, n_tok, act, st);
-    return vec ? launch_up<bf16, true>(x, W, wgu, idx, mid, ff, top, n_tok, act, st)
-               : launch_up<bf16, false>(x, W, wgu, idx, mid, ff, top, n_tok, act, st);
+        return vec ? launch_up<float, true>(x, W, wgu, idx, mid, ff, top, n_tok, act, in_wt, limit, st)
+                   : launch_up<float, false>(x, W, wgu, idx, mid, ff, top, n_tok, act, in_wt, limit, st);
+    return vec ? launch_up<bf16, true>(x, W, wgu, idx, mid, ff, top, n_tok, act, in_wt, limit, st)
+               : launch_up<bf16, false>(x, W, wgu, idx, mid, ff, top, n_tok, act, in_wt, limit, st);
 }
 
 DK_EXPORT int dk_moe_down_rows(int dtype, const void* mid, const void* wd, const int* idx, const float* wt,

@@ -80,7 +80,7 @@ moe_sort_kernel(const int* idx, int P, int E, int* perm, int* inv, int* tiles, i
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* tiles, const int* perm, int top, bf16* out,
-                        int N, int K, int act) {
+                        int N, int K, int act, const float* in_wt, float limit) {
     extern __shared__ __align__(16) bf16 mt_smem[];
     constexpr int A_ELEMS = MT_ROWS * MT_STR, B_ELEMS = (GATED ? 2 : 1) * MT_COLS * MT_STR;
     bf16* As = mt_smem;                              // [MT_STAGES][A_ELEMS]
@@ -171,9 +171,20 @@ moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* ti
                 if (r < rows && n < N) {
                     float v = accg[m][nt][c];
                     if (GATED) {
-                        const float u = accu[m][nt][c];
-                        v = (act == 1 ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
-                                      : v / (1.f + expf(-v))) * u;
+                        float u = accu[m][nt][c];
+                        if (in_wt != nullptr) {      // the pair's weight on the expert's input: W (w x) = w (W x)
+                            const float w = in_wt[perm[first + r]];
+                            v *= w;
+                            u *= w;
+                        }
+                        if (act == 2) {              // g' = min(g, limit), u' = clamp(u): g' sigmoid(1.702 g') (u' + 1)
+                            v = fminf(v, limit);
+                            u = fminf(fmaxf(u, -limit), limit);
+                            v = v / (1.f + expf(-1.702f * v)) * (u + 1.f);
+                        } else {
+                            v = (act == 1 ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                                          : v / (1.f + expf(-v))) * u;
+                        }
                     }
                     out[(size_t)(first + r) * N + n] = __float2bfloat16_rn(v);
                 }
@@ -189,7 +200,7 @@ __global__ void moe_sum_kernel(const bf16* y, const int* inv, const float* wt, c
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = 0.f;
-        for (int j = 0; j < top; j++) acc = fmaf(wt[t * top + j], __bfloat162float(y[(size_t)inv[t * top + j] * W + c]), acc);
+        for (int j = 0; j < top; j++) acc = fmaf(wt != nullptr ? wt[t * top + j] : 1.f, __bfloat162float(y[(size_t)inv[t * top + j] * W + c]), acc);
         if (shared != nullptr) acc = fmaf(sgate ? sgate[t] : 1.f, __bfloat162float(shared[t * W + c]), acc);
         out[t * W + c] = __float2bfloat16_rn(acc);
     }
@@ -201,7 +212,7 @@ DK_EXPORT int dk_moe_sort(const int* idx, int P, int E, int* perm, int* inv, int
 }
 
 DK_EXPORT int dk_moe_up_tiles(const void* x, const void* wgu, const int* tiles, int max_tiles, const int* perm, int top, void* mid,
-                              int ff, int W, int act, cudaStream_t st) {
+                              int ff, int W, int act, const float* in_wt, float limit, cudaStream_t st) {
     if (W % MT_KC || ((uintptr_t)x | (uintptr_t)wgu) % 16) return (int)cudaErrorInvalidValue;
     constexpr size_t smem = sizeof(bf16) * MT_STAGES * (MT_ROWS + 2 * MT_COLS) * MT_STR;
     static bool attr = false;
@@ -211,7 +222,7 @@ DK_EXPORT int dk_moe_up_tiles(const void* x, const void* wgu, const int* tiles, 
         attr = true;
     }
     return dk_launch(moe_tile_product_kernel<true>, dim3(max_tiles, (ff + MT_COLS - 1) / MT_COLS), dim3(128), smem, st, (const bf16*)x,
-                     (const bf16*)wgu, tiles, perm, top, (bf16*)mid, ff, W, act);
+                     (const bf16*)wgu, tiles, perm, top, (bf16*)mid, ff, W, act, in_wt, limit);
 }
 
 DK_EXPORT int dk_moe_down_tiles(const void* mid, const void* wd, const int* tiles, int max_tiles, void* y, int W, int ff,
@@ -225,7 +236,7 @@ DK_EXPORT int dk_moe_down_tiles(const void* mid, const void* wd, const int* tile
         attr = true;
     }
     return dk_launch(moe_tile_product_kernel<false>, dim3(max_tiles, (W + MT_COLS - 1) / MT_COLS), dim3(128), smem, st, (const bf16*)mid,
-                     (const bf16*)wd, tiles, (const int*)nullptr, 1, (bf16*)y, W, ff, 0);
+                     (const bf16*)wd, tiles, (const int*)nullptr, 1, (bf16*)y, W, ff, 0, (const float*)nullptr, 0.f);
 }
 
 DK_EXPORT int dk_moe_sum(const void* y, const int* inv, const float* wt, const void* shared, const float* sgate, void* out,

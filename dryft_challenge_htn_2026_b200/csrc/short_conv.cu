@@ -9,7 +9,13 @@
 //     with i + rot_dims / 2) by angles from a table [positions, rot_dims / 2]; the rest pass,
 //   * values blended with another layer's values of the same token: v <- (1 - lam) v + lam v_src, lam a
 //     learned number on the device.
-// Each option may be left out (taps = 1, norm_mode 0, rot_dims = 0, no v_src). The result is a dense row
+//   * a bias per channel of q, k and v (float32 [channels]), added to the projection (behind the convolution,
+//     before the norm),
+//   * a query temperature: every q head times 1 + coef * ln(floor((p + 1) / every) + 1) at position p (last of all),
+//   * query heads split into q_split equal parts: each part becomes a query head of the full size of its own
+//     that holds the part at its place and zeros elsewhere (out then has q_split * nh query heads), so that a
+//     key row made of q_split maps side by side is scored one map at a time by ordinary attention.
+// Each option may be left out (taps = 1, norm_mode 0, rot_dims = 0, no v_src, no bias, every = 0, q_split = 1). The result is a dense row
 // [q heads | k heads | v heads] in the storage type; sums, norms and the rotation are float32. Given the paged
 // key and value stores, the kernel also writes each token's k and v heads to their place there (the step's cache write).
 // A second kernel moves the state on once the first has read it.
@@ -17,6 +23,16 @@
 
 #define SC_THREADS 128
 #define SC_MAX_TAPS 9
+
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+    return 1.f + coef * logf((float)((pos + 1) / every) + 1.f);
+}
+// coordinate d of a query head of size hd into its part's head (of the parts heads that stand for it), zeros into the others
+template <typename T>
+__device__ __forceinline__ void write_split(T* heads, int d, int hd, int parts, T value) {
+    const int part = d / (hd / parts);
+    for (int m = 0; m < parts; m++) heads[(size_t)m * hd + d] = m == part ? value : from_f<T>(0.f);
+}
 
 // One block per (token row, head of q, k or v). Rows with position < 0 are padding.
 template <typename T>
@@ -26,7 +42,8 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
                       const float* __restrict__ vmix, const T* v_src, long long ld_src,
                       const float* __restrict__ cosv, const float* __restrict__ sinv, int rot_dims, const int* row_pos,
                       const int* row_seq, const int* seq_pos0, const int* seq_slot, int nh, int nkv, int hd, int hdv,
-                      T* k_store, T* v_store, const int* page_table, int pt_stride) {
+                      T* k_store, T* v_store, const int* page_table, int pt_stride, const float* __restrict__ bias,
+                      float qt_coef, int qt_every, int q_split) {
     __shared__ float red[33];
     __shared__ float ys[256];
     pdl_wait();
@@ -62,6 +79,7 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
                 const float w = taps > 1 ? to_f(wconv[(size_t)c * taps + j]) : 1.f;
                 acc = fmaf(w, u, acc);
             }
+            if (bias != nullptr) acc += bias[c];
             y[r] = acc;
             ss += acc * acc;
         }
@@ -127,12 +145,15 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
             cached = head < nh + nkv ? k_store + kv_offset(page, nkv, head - nh, pos % DK_PAGE, hd)
                                      : v_store + kv_offset(page, nkv, head - nh - nkv, pos % DK_PAGE, hdv);
     }
+    const float temp = head < nh && qt_every > 0 ? query_temperature(pos, qt_coef, qt_every) : 1.f;
+    const int shift = (q_split - 1) * nh * hd;     // k and v stand behind q_split * nh query heads in ``out``
 #pragma unroll
     for (int r = 0; r < 2; r++) {
         const int d = threadIdx.x + r * SC_THREADS;
         if (d < size) {
-            const T o = from_f<T>(y[r]);
-            out[(size_t)t * ldo + c0 + d] = o;
+            const T o = from_f<T>(y[r] * temp);
+            if (head < nh && q_split > 1) write_split(out + (size_t)t * ldo + (size_t)head * q_split * hd, d, hd, q_split, o);
+            else out[(size_t)t * ldo + c0 + (head < nh ? 0 : shift) + d] = o;
             if (cached != nullptr) cached[d] = o;
         }
     }
@@ -148,7 +169,8 @@ norm_rope_rows_kernel(const T* proj, long long ld, T* out, long long ldo, int no
                       const float* __restrict__ kn, float eps, const float* __restrict__ vmix, const T* v_src,
                       long long ld_src, const float* __restrict__ cosv, const float* __restrict__ sinv, int rot_dims,
                       const int* row_pos, const int* row_seq, int n_tok, int nh, int nkv, int hd, int hdv, T* k_store,
-                      T* v_store, const int* page_table, int pt_stride) {
+                      T* v_store, const int* page_table, int pt_stride, const float* __restrict__ bias, float qt_coef,
+                      int qt_every, int q_split) {
     __shared__ float ys_all[SC_ROW_WARPS][256];
     pdl_wait();
     pdl_launch_dependents();
@@ -172,7 +194,7 @@ norm_rope_rows_kernel(const T* proj, long long ld, T* out, long long ldo, int no
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int d = lane + 32 * i;
-        y[i] = d < size ? to_f(src[d]) : 0.f;
+        y[i] = d < size ? to_f(src[d]) + (bias != nullptr ? bias[c0 + d] : 0.f) : 0.f;
         ss += y[i] * y[i];
     }
     if (qk && norm_mode == 1) {
@@ -228,13 +250,15 @@ norm_rope_rows_kernel(const T* proj, long long ld, T* out, long long ldo, int no
             cached = head < nh + nkv ? k_store + kv_offset(page, nkv, head - nh, pos % DK_PAGE, hd)
                                      : v_store + kv_offset(page, nkv, head - nh - nkv, pos % DK_PAGE, hdv);
     }
-    T* dst = out + (size_t)t * ldo + c0;
+    const float temp = head < nh && qt_every > 0 ? query_temperature(pos, qt_coef, qt_every) : 1.f;
+    T* dst = out + (size_t)t * ldo + c0 + (head < nh ? 0 : (q_split - 1) * nh * hd);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int d = lane + 32 * i;
         if (d < size) {
-            const T o = from_f<T>(y[i]);
-            dst[d] = o;
+            const T o = from_f<T>(y[i] * temp);
+            if (head < nh && q_split > 1) write_split(out + (size_t)t * ldo + (size_t)head * q_split * hd, d, hd, q_split, o);
+            else dst[d] = o;
             if (cached != nullptr) cached[d] = o;
         }
     }
@@ -270,8 +294,9 @@ DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void*
                                 const float* vmix, const void* v_src, long long ld_src, const float* cosv, const float* sinv, int rot_dims, const int* row_pos,
                                 const int* row_seq, const int* seq_pos0, const int* seq_slot, int n_tok, int nh, int nkv,
                                 int hd, int hdv, void* k_store, void* v_store, const int* page_table, int pt_stride,
-                                cudaStream_t st) {
-    if (hd > 256 || hdv > 256 || taps < 1 || taps > SC_MAX_TAPS || rot_dims > hd || rot_dims % 2)
+                                const float* bias, float qt_coef, int qt_every, int q_split, cudaStream_t st) {
+    if (hd > 256 || hdv > 256 || taps < 1 || taps > SC_MAX_TAPS || rot_dims > hd || rot_dims % 2 || q_split < 1 ||
+        hd % q_split || qt_every < 0)
         return (int)cudaErrorInvalidValue;
     if (taps == 1) {
         const long long items = (long long)n_tok * (nh + 2 * nkv);
@@ -279,19 +304,22 @@ DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void*
         if (dtype == 0)
             return dk_launch(norm_rope_rows_kernel<float>, rgrid, rblock, 0, st, (const float*)proj, ld, (float*)out, ldo,
                              norm_mode, qn, kn, eps, vmix, (const float*)v_src, ld_src, cosv, sinv, rot_dims, row_pos,
-                             row_seq, n_tok, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride);
+                             row_seq, n_tok, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride, bias, qt_coef,
+                             qt_every, q_split);
         return dk_launch(norm_rope_rows_kernel<bf16>, rgrid, rblock, 0, st, (const bf16*)proj, ld, (bf16*)out, ldo, norm_mode,
                          qn, kn, eps, vmix, (const bf16*)v_src, ld_src, cosv, sinv, rot_dims, row_pos, row_seq, n_tok, nh,
-                         nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride);
+                         nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride, bias, qt_coef, qt_every, q_split);
     }
     const dim3 grid(n_tok, nh + 2 * nkv), block(SC_THREADS);
     if (dtype == 0)
         return dk_launch(conv_norm_rope_kernel<float>, grid, block, 0, st, (const float*)proj, ld, (float*)out, ldo,
                          (const float*)state, (const float*)wconv, taps, norm_mode, qn, kn, eps, vmix, (const float*)v_src, ld_src, cosv, sinv, rot_dims, row_pos,
-                         row_seq, seq_pos0, seq_slot, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride);
+                         row_seq, seq_pos0, seq_slot, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride,
+                         bias, qt_coef, qt_every, q_split);
     return dk_launch(conv_norm_rope_kernel<bf16>, grid, block, 0, st, (const bf16*)proj, ld, (bf16*)out, ldo,
                      (const bf16*)state, (const bf16*)wconv, taps, norm_mode, qn, kn, eps, vmix, (const bf16*)v_src, ld_src, cosv, sinv, rot_dims, row_pos, row_seq,
-                     seq_pos0, seq_slot, nh, nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride);
+                     seq_pos0, seq_slot, nh, nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride, bias, qt_coef,
+                     qt_every, q_split);
 }
 
 DK_EXPORT int dk_conv_state_update(int dtype, const void* proj, long long ld, void* state, int taps, int C,

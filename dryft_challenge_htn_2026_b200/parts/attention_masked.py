@@ -55,7 +55,17 @@ class MaskedAttention(Part):
         self.position = build_part(s.position, rt) if s.position is not None else None
         if self.position is not None and self.position.spec.dim > s.head_dim:
             raise ValueError(f"a rotation over {self.position.spec.dim} coordinates of heads of {s.head_dim}")
-        self.prepares = self.taps > 1 or self.qk_norm is not None or self.position is not None or s.value_mix is not None
+        if s.talk and (s.chunk is not None or s.distance_bias or s.sink or s.unit_sink or s.output_gate or s.keep_first
+                       or s.softcap is not None or s.values_in_keys):
+            raise ValueError("attention with mixed head scores takes a window and nothing else of the masks and options")
+        if s.talk and (s.num_heads > api.TALK_MAX_HEADS or s.num_heads * s.v_head_dim > api.TALK_MAX_OUT):
+            raise ValueError(f"attention with mixed head scores takes up to {api.TALK_MAX_HEADS} heads and heads x value size "
+                             f"up to {api.TALK_MAX_OUT}")
+        if s.q_temp is not None and not (int(s.q_temp[1]) >= 1):
+            raise ValueError(f"a query temperature every {s.q_temp[1]} positions")
+        self.bias = self.talk = None
+        self.prepares = self.taps > 1 or self.qk_norm is not None or self.position is not None or s.value_mix is not None \
+            or s.bias or s.q_temp is not None
         self.n_qkv = self.n_q + self.n_k + self.n_v
         self.q_norm_w = self.k_norm_w = self.w_conv = None
         self.max_positions = 0
@@ -97,6 +107,12 @@ class MaskedAttention(Part):
                   ParamDecl("k.norm", (s.head_dim,), init="norm", keep_float32=True)]
         if s.value_mix is not None:
             d.append(ParamDecl("vmix", (), init="fraction", keep_float32=True))
+        if s.bias:
+            d += [ParamDecl("q.b", (self.n_q,), init="around_zero", keep_float32=True),
+                  ParamDecl("k.b", (self.n_k,), init="around_zero", keep_float32=True),
+                  ParamDecl("v.b", (self.n_v,), init="around_zero", keep_float32=True)]
+        if s.talk:
+            d.append(ParamDecl("talk", (s.num_heads, s.num_heads), init="near_identity", keep_float32=True))
         return d
 
     def bind(self, tensors):
@@ -117,6 +133,10 @@ class MaskedAttention(Part):
             self.k_norm_w = tensors.pop("k.norm").to(torch.float32).contiguous()
         if self.spec.value_mix is not None:
             self.v_mix = tensors.pop("vmix").to(torch.float32).reshape(1).contiguous()
+        if self.spec.bias:
+            self.bias = torch.cat([tensors.pop(n).to(torch.float32).reshape(-1) for n in ("q.b", "k.b", "v.b")]).contiguous()
+        if self.spec.talk:
+            self.talk = tensors.pop("talk").to(torch.float32).contiguous()
 
     def step_weights(self):
         return [self.w_in, self.w_o]
@@ -160,7 +180,7 @@ class MaskedAttention(Part):
                            pos0, ctx.seq_slot, s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim,
                            views[0].k if writes else None, views[0].v if writes else None,
                            ctx.tables[views[0].group] if writes else None, norm_mode=norm_mode,
-                           v_mix=self.v_mix if v_src is not None else None, v_src=v_src)
+                           v_mix=self.v_mix if v_src is not None else None, v_src=v_src, bias=self.bias, q_temp=s.q_temp)
         if s.value_mix == "source":      # this step's values, for the layers that blend theirs with them
             ctx.carry[("value_mix", self.n_v)] = out[:, self.n_q + self.n_k:]
         if self.taps > 1:
@@ -185,6 +205,11 @@ class MaskedAttention(Part):
         ``k`` and ``v`` rows go into the cache first. Picks the kernel by type, phase and head sizes."""
         s = self.spec
         table = ctx.tables[kv.group]
+        if self.talk is not None:     # mixed head scores: one kernel for every phase and type
+            if writes:
+                api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
+            return api.attention_talk(q, mid, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_heads, s.num_kv_heads,
+                                      s.head_dim, s.v_head_dim, s.window, s.scale, self.talk)
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
         if self.tensor_core and ctx.is_decode and not s.values_in_keys \
                 and api.masked_decode_streams(q, mid, gate, s.head_dim, s.v_head_dim):

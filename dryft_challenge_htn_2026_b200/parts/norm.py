@@ -1,7 +1,7 @@
 """RMSNorm (reference: engine/engine.py:107-110, engine/fused.py:152-172)."""
 import torch
 
-from ..config.specs import OnePlusRMSNormSpec, RMSNormSpec, ScalarRMSNormSpec
+from ..config.specs import GroupRMSNormSpec, OnePlusRMSNormSpec, RMSNormSpec, ScalarRMSNormSpec
 from ..csrc import api
 from .base import ParamDecl, Part, register_part
 
@@ -80,3 +80,28 @@ class OnePlusRMSNorm(RMSNorm):
 
 
 register_part(OnePlusRMSNormSpec, OnePlusRMSNorm)
+
+
+class GroupRMSNorm(Part):
+    """RMS norm in groups: the row in ``groups`` equal consecutive parts, each over its own root mean square, the whole
+    times a weight of the row's size. Statistics in float32, weight held in float32; one kernel with the residual add,
+    also gathered at the wanted rows (so it can stand as first, inner and final norm)."""
+    takes_partial = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if spec.groups < 1 or spec.dim % spec.groups:
+            raise ValueError(f"a norm in {spec.groups} parts of {spec.dim} coordinates")
+
+    def param_decls(self):
+        return [ParamDecl(self.spec.tensor, (self.spec.dim,), init="norm", keep_float32=True)]
+
+    def bind(self, tensors):
+        self.weight = tensors[self.spec.tensor].to(torch.float32).contiguous()
+
+    def add_forward(self, h, delta, out, rows=None):
+        api.add_group_rmsnorm(h, delta, self.weight, self.spec.eps, self.spec.groups, out, rows)
+        return out
+
+
+register_part(GroupRMSNormSpec, GroupRMSNorm)

@@ -4,6 +4,7 @@ class. The config class turns config.json into a ``ModelSpec``; the parts regist
 Adding an architecture: write a ``ModelConfig`` subclass with ``architecture``, ``from_dict``,
 ``to_dict`` and ``to_spec``, then ``register_architecture(YourConfig)``."""
 from .config.base import ConfigError, read_config_json
+from .config.nevotar import NevotarConfig
 from .config.nilivik import NilivikConfig
 from .config.pibulix import PibulixConfig
 from .config.qwen3 import Qwen3Config
@@ -47,3 +48,4 @@ register_architecture(Qwen3Config)
 register_architecture(NilivikConfig)
 register_architecture(PibulixConfig)
 register_architecture(VenidraConfig)
+register_architecture(NevotarConfig)

@@ -26,6 +26,8 @@ def _shape_draw(x, init, matrix_std, norm_std):
         return 0.5 * x
     if init == "fraction":          # a blending weight between 0 and 1
         return torch.sigmoid(x)
+    if init == "near_identity":     # a square matrix that mixes channels a little: the identity plus noise
+        return torch.eye(x.shape[-1], dtype=x.dtype, device=x.device) + 0.3 * x
     if init == "wide":              # matrices whose outputs should spread (routers, the second step of a decay)
         return 10.0 * matrix_std * x
     return matrix_std * x
