@@ -64,25 +64,31 @@ def diff_lambda(p, diff):
     return float(torch.exp((p["lq1"] * p["lk1"]).sum()) - torch.exp((p["lq2"] * p["lk2"]).sum()) + diff)
 
 
+def diff_core(q, k, v, scale, lam, diff, eps, q_temp=None, pos0=0):
+    """q [T, H, 2, D], k [T, G, 2, D], v [T, G, V] -> [T, H, V]: per head two causal softmax maps over the same values,
+    a1 - lam a2, over the head's root mean square, times 1 - diff."""
+    T, H = q.shape[:2]
+    G, V = k.shape[1], v.shape[2]
+    if q_temp:
+        q = q * query_temperature(torch.arange(pos0, pos0 + T), q_temp["coef"], q_temp["every"])[:, None, None, None]
+    see = causal(T)
+    out = torch.zeros(T, H, V, dtype=F)
+    for hd in range(H):
+        g = hd // (H // G)
+        a = [softmax_rows((q[:, hd, j] @ k[:, g, j].T) * scale, see) @ v[:, g] for j in range(2)]
+        out[:, hd] = rms(a[0] - lam * a[1], eps) * (1.0 - diff)
+    return out
+
+
 def diff_attention(h, p, m, eps, pos0=0):
     """Two softmax maps per head over the same values, combined as a1 - lambda a2, each head then over its root
     mean square, times 1 - diff."""
     T = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    pos = torch.arange(pos0, pos0 + T)
     q = (h @ p["q"].T + p["q.b"]).reshape(T, H, 2, D)
     k = (h @ p["k"].T + p["k.b"]).reshape(T, G, 2, D)
     v = (h @ p["v"].T + p["v.b"]).reshape(T, G, V)
-    qt = m.get("q_temp")
-    if qt:
-        q = q * query_temperature(pos, qt["coef"], qt["every"])[:, None, None, None]
-    lam = diff_lambda(p, m["diff"])
-    see = causal(T)
-    out = torch.zeros(T, H, V, dtype=F)
-    for hd in range(H):
-        g = hd // (H // G)
-        a = [softmax_rows((q[:, hd, j] @ k[:, g, j].T) * m["scale"], see) @ v[:, g] for j in range(2)]
-        out[:, hd] = rms(a[0] - lam * a[1], eps) * (1.0 - m["diff"])
+    out = diff_core(q, k, v, m["scale"], diff_lambda(p, m["diff"]), m["diff"], eps, m.get("q_temp"), pos0)
     return out.reshape(T, H * V) @ p["o"].T
 
 
@@ -116,13 +122,21 @@ def talking_window_attention(h, p, m, eps, pos0=0):
     rot = m.get("rot")
     if rot and rot["dims"]:
         q, k = rotate_partial(q, pos, rot["dims"], rot["base"]), rotate_partial(k, pos, rot["dims"], rot["base"])
-    s = torch.stack([(q[:, hd] @ k[:, hd // (H // G)].T) * m["scale"] for hd in range(H)], 0)       # [H, T, T]
-    s = torch.einsum("hg,gij->hij", p["talk"], s)
-    see = causal(T, m["mask"]["size"] if m.get("mask") else None)
+    out = talking_core(q, k, v, p["talk"], m["scale"], m["mask"]["size"] if m.get("mask") else None)
+    return out.reshape(T, H * V) @ p["o"].T
+
+
+def talking_core(q, k, v, talk, scale, window):
+    """q [T, H, D], k [T, G, D], v [T, G, V] -> [T, H, V]: score_h <- sum_g talk[h, g] score_g, then the window and the softmax."""
+    T, H = q.shape[:2]
+    G, V = k.shape[1], v.shape[2]
+    s = torch.stack([(q[:, hd] @ k[:, hd // (H // G)].T) * scale for hd in range(H)], 0)       # [H, T, T]
+    s = torch.einsum("hg,gij->hij", talk, s)
+    see = causal(T, window)
     out = torch.zeros(T, H, V, dtype=F)
     for hd in range(H):
         out[:, hd] = softmax_rows(s[hd], see) @ v[:, hd // (H // G)]
-    return out.reshape(T, H * V) @ p["o"].T
+    return out
 
 
 def conv_taps(u, w, b, before=None):
@@ -205,6 +219,18 @@ def mixer(kind, a, p, m, eps, pos0=0, state=None):
         right, state = ssd(a, sub(p, "right."), m["right"], eps, state)
         return m["left_scale"] * left + m["right_scale"] * right, state
     raise ValueError(kind)
+
+
+def read_model(folder):
+    """(config.json as a dict, tensors by name) of a model folder."""
+    import json
+    import os
+
+    from safetensors.torch import load_file
+
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(folder, "model.safetensors"))
 
 
 def forward(tokens, tensors, cfg, taps=None):
