@@ -1490,3 +1490,64 @@ def attention_talk(q, out, out_scale, k_store, v_store, row_pos, row_seq, page_t
                                       _p(k_store), _p(v_store), _p(row_pos), _p(row_seq), _p(page_table), page_table.shape[1],
                                       q.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, int(window or 0), c_float(scale),
                                       _p(talk), _stream()), "attention_talk")
+
+
+TALK_TILE_ROWS = 16           # queries a block of attention_talk_bf16 takes
+TALK_MAX_SPLITS = 16
+_TALK_SMEM = 220 * 1024
+
+
+def _talk_lib(head_dim, v_head_dim):
+    return _lib("attention_talk_bf16.cu", {"HD": head_dim, "HDV": v_head_dim})
+
+
+def talk_bf16_takes(n_heads, n_kv_heads, head_dim, v_head_dim):
+    """Whether the tensor-core form of attention with mixed head scores takes these sizes: key and value sizes in steps
+    of 16 up to 256, and a run of 32 keys and values of every kv head beside the heads' score tiles in shared memory."""
+    if head_dim % 16 or v_head_dim % 16 or max(head_dim, v_head_dim) > 256 or n_heads > TALK_MAX_HEADS:
+        return False
+    smem = 2 * n_kv_heads * 32 * (head_dim + 8 + v_head_dim + 8) + 4 * (n_heads * 16 * 34 + n_heads * n_heads)
+    return smem <= _TALK_SMEM
+
+
+def talk_operands(q, out):
+    """Rows the tensor-core kernel can read and write two numbers at a time."""
+    return all(t.stride(0) % 2 == 0 and t.data_ptr() % 4 == 0 for t in (q, out))
+
+
+def talk_decode_splits(rows, n_heads, table_pages, window):
+    """Runs of keys a single-token step of attention_talk_bf16 deals out over blocks: enough blocks for the GPU, no more
+    than there are runs of 32 keys in sight; a function of the step's shape alone (a captured graph keeps it)."""
+    keys = table_pages * PAGE if not window else min(window + 32, table_pages * PAGE)
+    runs = max(1, (keys + 31) // 32)
+    blocks = rows * ((n_heads + 15) // 16)
+    return max(1, min(TALK_MAX_SPLITS, runs, (2 * sm_count() + blocks - 1) // blocks))
+
+
+def talk_decode_ws(rows, n_heads, v_head_dim, nsplit, device):
+    return (torch.empty((rows, n_heads, nsplit, v_head_dim), dtype=torch.float32, device=device),
+            torch.empty((rows, n_heads, nsplit, 2), dtype=torch.float32, device=device))
+
+
+def attention_talk_bf16(q, out, out_scale, k_store, v_store, page_table, n_heads, n_kv_heads, head_dim, v_head_dim, window, scale, talk,
+                        tiles=None, cu_q=None, seq_pos0=None, row_pos=None, nsplit=1, ws=None):
+    """``attention_talk`` on mma.sync tensor cores, bfloat16. Prompts and portions: ``tiles`` (the ``QueryTiles(16)`` plan), ``cu_q``,
+    ``seq_pos0``. Single tokens: ``row_pos`` (row r is sequence r, -1: padding), the keys in ``nsplit`` runs with ``ws`` from
+    ``talk_decode_ws`` when nsplit > 1."""
+    _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16), _need(talk, "talk", torch.float32, 2)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", torch.bfloat16), _need(v_store, "v_store", torch.bfloat16)
+    _need(tiles, "tiles", torch.int32), _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1)
+    _need(row_pos, "row_pos", torch.int32, 1)
+    if not talk_bf16_takes(n_heads, n_kv_heads, head_dim, v_head_dim) or n_heads % n_kv_heads or tuple(talk.shape) != (n_heads, n_heads) or \
+            q.shape[1] != n_heads * head_dim or out.shape != (q.shape[0], n_heads * v_head_dim) or not talk_operands(q, out) or \
+            (tiles is None) == (row_pos is None) or (tiles is not None and (cu_q is None or seq_pos0 is None or nsplit != 1)) or \
+            (nsplit > 1 and (ws is None or ws[0].shape != (q.shape[0], n_heads, nsplit, v_head_dim))):
+        raise KernelError("attention_talk_bf16: sizes or operands the kernel does not take")
+    n_tiles = tiles.numel() // 2 if tiles is not None else q.shape[0]
+    lib = _talk_lib(head_dim, v_head_dim)
+    _check(lib, lib.dk_attention_talk_bf16(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), c_float(out_scale),
+                                           _p(k_store), _p(v_store), _p(tiles), n_tiles, _p(cu_q), _p(seq_pos0), _p(row_pos),
+                                           _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0), c_float(scale),
+                                           _p(talk), int(nsplit), _p(ws[0]) if ws is not None else c_void_p(0),
+                                           _p(ws[1]) if ws is not None else c_void_p(0), _stream()),
+           "attention_talk_bf16", 2 if nsplit > 1 else 1)

@@ -134,5 +134,6 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
     jobs += [("attention_bf16.cu", {"HD": hd, "DK_MASKED": 1}) for hd in head_dims if hd in (64, 128)]
     jobs += [("attention_masked_bf16.cu", {"HD": hd, "HDV": hd}) for hd in head_dims if hd in (64, 128)]
     jobs += [("linear_attention_bf16.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]
+    jobs += [("attention_talk_bf16.cu", {"HD": hd, "HDV": hd}) for hd in head_dims if hd in (64, 128)]
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
         return list(ex.map(lambda j: compile_lib(j[0], j[1], verbose), jobs))

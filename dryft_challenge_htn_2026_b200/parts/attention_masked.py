@@ -84,9 +84,12 @@ class MaskedAttention(Part):
         # equal head sizes of 64 or 128: prompts run on the tcgen05 kernel (its masked build), in tiles of 128 queries
         self.tc_tiles = QueryTiles(api.TC_TILE_ROWS) if self.tensor_core and s.head_dim == s.v_head_dim \
             and s.head_dim in api.TC_ATTENTION_HEAD_DIMS and not s.values_in_keys else None
+        # mixed head scores in bfloat16 with sizes in steps of 16: tiles of 16 queries with all their heads on mma.sync
+        self.talk_tiles = QueryTiles(api.TALK_TILE_ROWS) if s.talk and rt.dtype == torch.bfloat16 and \
+            api.talk_bf16_takes(s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim) else None
 
     def step_plans(self):
-        return [t for t in (self.tiles, self.tc_tiles, self.row_tiles) if t is not None]
+        return [t for t in (self.tiles, self.tc_tiles, self.row_tiles, self.talk_tiles) if t is not None]
 
     def param_decls(self):
         s = self.spec
@@ -205,9 +208,19 @@ class MaskedAttention(Part):
         ``k`` and ``v`` rows go into the cache first. Picks the kernel by type, phase and head sizes."""
         s = self.spec
         table = ctx.tables[kv.group]
-        if self.talk is not None:     # mixed head scores: one kernel for every phase and type
+        if self.talk is not None:     # mixed head scores: the tensor-core kernel, or the float32-arithmetic one for every phase and type
             if writes:
                 api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
+            if self.talk_tiles is not None and api.talk_operands(q, mid):
+                sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.scale, self.talk)
+                if not ctx.is_decode:
+                    return api.attention_talk_bf16(q, mid, scale, kv.k, kv.v, table, *sizes, tiles=ctx.plans[self.talk_tiles.key],
+                                                   cu_q=ctx.cu_q, seq_pos0=ctx.seq_pos0)
+                nsplit = api.talk_decode_splits(ctx.n_tok, s.num_heads, table.shape[1], s.window)
+                ws = ctx.scratch(("talk_decode", ctx.n_tok, s.num_heads, s.v_head_dim, nsplit),
+                                 lambda: api.talk_decode_ws(ctx.n_tok, s.num_heads, s.v_head_dim, nsplit, self.rt.device)) \
+                    if nsplit > 1 else None
+                return api.attention_talk_bf16(q, mid, scale, kv.k, kv.v, table, *sizes, row_pos=ctx.row_pos, nsplit=nsplit, ws=ws)
             return api.attention_talk(q, mid, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_heads, s.num_kv_heads,
                                       s.head_dim, s.v_head_dim, s.window, s.scale, self.talk)
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)

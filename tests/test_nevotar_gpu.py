@@ -259,7 +259,7 @@ def talk_spec(H, G, D, V, window, rot, W=8):
 
 
 TALK_SHAPES = [(4, 2, 32, 16, 24, (16, 10000.0)), (3, 3, 16, 48, 64, None), (8, 4, 64, 32, 100, (64, 250000.0)), (3, 1, 20, 10, 33, (10, 100.0)),
-               (2, 1, 128, 128, None, (32, 10000.0)), (2, 2, 12, 12, 1, None), (16, 2, 48, 96, 70, (48, 1e6))]
+               (2, 1, 128, 128, None, (32, 10000.0)), (2, 2, 12, 12, 1, None), (16, 2, 48, 96, 70, (48, 1e6)), (20, 4, 32, 16, 50, None)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -358,10 +358,12 @@ def test_state_space_mixer_in_prompts_portions_and_single_tokens(dtype, H, V, N,
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_state_space_mixer_keeps_far_tokens_when_steps_are_small(dtype):
-    """A strongly negative dt_bias makes every step small, so the decay stays near one over 900 tokens."""
+    """A strongly negative dt_bias makes every step small, so the decay stays near one over 900 tokens (the norm behind
+    the state brings the small writes back to size)."""
     H, V, N, W = 2, 16, 32, 24
     spec = StateSpaceSpec(hidden_size=W, num_heads=H, v_head_dim=V, state_dim=N, groups=1, conv_taps=3, norm_groups=1, norm_eps=1e-5)
-    part, p = bound_part(spec, dtype, seed=13, scale=0.15, dt_bias=torch.full((H,), -8.0), A_log=torch.zeros(H))
+    part, p = bound_part(spec, dtype, seed=13, scale=0.15, dt_bias=torch.full((H,), -8.0), A_log=torch.zeros(H),
+                         D=torch.zeros(H))       # no skip: the output is what the state gives
     x = rnd(930, W, seed=14).to(dtype).double()
     m = {"heads": H, "vdim": V, "state": N, "groups": 1, "norm_groups": 1}
     ref, _ = plain.ssd(x, p, m, 1e-5)
