@@ -796,8 +796,166 @@ def venidra_kernel_times(torch, dk, pk, cfg_d, heads, kv_heads):
     return out
 
 
+NEVOTAR_WINDOW = 1024
+
+
+def nevotar_config(width, heads, kv_heads, ff_qwen, layers, vocab):
+    """A Nevotar model of Qwen3's width, layer count and feed-forward arithmetic: differential attention of half Qwen3's
+    head counts (two maps of 64 side by side, values of 128, a temperature every 64 positions), an HGRN2 layer of as many
+    heads of 128, and layers that run attention with mixed head scores (heads of 128, half the head rotated, a window of
+    1,024) beside a state-space mixer as wide as the model (heads of 128, states of 128, 4 groups, 4 taps); every layer
+    with a mixture of 32 clamped experts of which a token uses 4, each a quarter of Qwen3's feed-forward, and a shared one."""
+    h2, g2 = heads // 2, max(1, kv_heads // 2)
+    eff = max(64, ff_qwen // 4 // 64 * 64)
+    mlp = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": 32, "top": 4}, "shared": {"ff": eff, "limit": 7.0}}
+    att = {"type": "attention", "mixer": {"heads": h2, "kv_heads": g2, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.6,
+                                          "q_temp": {"coef": 0.5, "every": 64}}, "mlp": mlp}
+    hg = {"type": "hgrn2", "mixer": {"heads": h2, "dim": 128, "vdim": 128}, "mlp": mlp}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": h2, "kv_heads": g2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 1e6},
+                              "mask": {"size": NEVOTAR_WINDOW}},
+                     "right": {"heads": width // 128, "vdim": 128, "state": 128, "groups": 4, "conv": 4, "norm_groups": 4},
+                     "left_scale": 0.6, "right_scale": 0.9}, "mlp": mlp}
+    return dict(architecture="Nevotar", vocab=vocab, width=width, norm={"eps": 1e-6, "groups": 2},
+                layers=[(att, hg, par, par)[i % 4] for i in range(layers)])
+
+
+def nevotar_kernel_times(torch, dk, pk, cfg_d, p_cfg):
+    """The design's mixer and feed-forward steps alone (the parts of a model of ``cfg_d``, so each step runs whichever kernel
+    the part picks), beside the like steps of the Pibulix model ``p_cfg`` of the same width: CUDA events around one step, L2
+    flushed before each (a 256 MB write), median of 5 after 2 untimed."""
+    from dryft_challenge_htn_2026_b200.cache import Cache
+    from dryft_challenge_htn_2026_b200.engine.batch import build_context
+    from dryft_challenge_htn_2026_b200.parts import Runtime, build_part
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for i in range(7):
+            flush.fill_(float(i))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[2:]) * 1e3        # microseconds
+
+    def flops_rec(us, flops):
+        return {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}
+
+    def bytes_rec(us, moved):
+        return {"us": round(us, 1), "gbs": round(moved / us / 1e3, 1), "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+
+    rt = Runtime(dev, bf)
+    g = torch.Generator(device=dev).manual_seed(1)
+    spec, pspec = dk.config_from_dict(cfg_d).to_spec(), dk.config_from_dict(p_cfg).to_spec()
+    W = spec.hidden_size
+
+    def bound(part_spec):
+        part = build_part(part_spec, rt)
+        part.bind({d.name: (torch.rand(d.shape, generator=g, device=dev) * 0.5 if d.init == "fraction" else
+                            torch.eye(d.shape[-1], device=dev) + 0.1 * torch.randn(d.shape, generator=g, device=dev) if d.init == "near_identity" else
+                            torch.randn(d.shape, generator=g, device=dev) * (0.2 if d.init == "wide" else 0.02) + (1.0 if d.init == "norm" else 0.0)).to(
+            torch.float32 if d.keep_float32 else bf) for d in part.param_decls()})
+        part.prepare(16384)
+        return part
+
+    diff, hg, par = bound(spec.layers[0].mixer), bound(spec.layers[1].mixer), bound(spec.layers[2].mixer)
+    talk, ssd = par.branches[0][1], par.branches[1][1]
+    moe, norm = bound(spec.layers[0].feed_forward), bound(spec.layers[0].norm_in)
+    p_att, p_gla = bound(pspec.layers[0].mixer), bound(pspec.layers[1].mixer)
+    p_moe, p_norm = bound(pspec.layers[1].feed_forward), bound(pspec.layers[0].norm_mix)
+    ds, ts_, ss, hs, ps = diff.spec, talk.spec, ssd.spec, hg.spec, p_att.spec
+    window = ts_.window
+    out = {}
+    scratch = {}
+
+    class Ctx:
+        def scratch(self, key, make):
+            if key not in scratch:
+                scratch[key] = make()
+            return scratch[key]
+
+    def fill(cache, n):
+        for e in range(n):
+            for v in cache.views(e):
+                if hasattr(v, "k"):
+                    v.k.normal_()
+                    if v.v is not None:
+                        v.v.normal_()
+
+    def steps(ctx, cache, rows, tag, pairs_full, pairs_win, keys_full, keys_win, keys_p):
+        """One record per step; ``pairs_*``: (query, key) pairs in sight in a prompt, ``keys_*``: keys a single token reads."""
+        mids = {n: torch.empty(rows, part.n_mid, dtype=bf, device=dev) for n, part in (("d", diff), ("t", talk), ("s", ssd), ("h", hg), ("pa", p_att), ("pg", p_gla))}
+        projs = {n: (torch.randn(rows, part.n_in, device=dev) * 0.5).to(bf) for n, part in (("d", diff), ("t", talk), ("s", ssd), ("h", hg), ("pa", p_att), ("pg", p_gla))}
+        ctx.carry = {}
+        H, D, V = ds.num_heads, ds.head_dim, ds.v_head_dim
+        us = timed(lambda: diff.mix(ctx, cache.views(0), projs["d"], mids["d"], 1.0))
+        out[f"differential_attention_{tag}"] = flops_rec(us, 4 * H * (D + V) * pairs_full) if pairs_full else \
+            dict(bytes_rec(us, rows * ds.num_kv_heads * keys_full * (2 * D + V) * 2), keys=keys_full)
+        H, D, V = ts_.num_heads, ts_.head_dim, ts_.v_head_dim
+        us = timed(lambda: talk.mix(ctx, cache.views(1)[:1], projs["t"], mids["t"], 1.0))
+        out[f"mixed_scores_attention_{tag}"] = flops_rec(us, 2 * H * (D + V) * pairs_win) if pairs_win else \
+            dict(bytes_rec(us, rows * ts_.num_kv_heads * keys_win * (D + V) * 2), keys=keys_win)
+        us = timed(lambda: p_att.mix(ctx, cache.views(3), projs["pa"], mids["pa"], 1.0))
+        out[f"pibulix_window_attention_{tag}"] = flops_rec(us, 4 * ps.num_heads * ps.head_dim * pairs_win) if pairs_win else \
+            dict(bytes_rec(us, rows * ps.num_kv_heads * keys_p * 2 * ps.head_dim * 2), keys=keys_p)
+        # the recurrences: what a prompt must move (operands in float32 in, outputs out), what a single token must (the state, twice)
+        us = timed(lambda: hg.mix(ctx, cache.views(2), projs["h"], mids["h"], 1.0))
+        out[f"lower_bound_recurrence_{tag}"] = bytes_rec(us, rows * hs.num_heads * (3 * hs.head_dim + 2 * hs.v_head_dim) * 4 if pairs_full else
+                                                         rows * hs.num_heads * hs.head_dim * hs.v_head_dim * 4 * 2)
+        us = timed(lambda: ssd.mix(ctx, cache.views(1)[1:], projs["s"], mids["s"], 1.0))
+        out[f"state_space_mixer_{tag}"] = bytes_rec(us, rows * (ss.num_heads * 2 * ss.v_head_dim + 2 * ss.groups * ss.state_dim) * 4 if pairs_full else
+                                                    rows * ss.num_heads * ss.state_dim * ss.v_head_dim * 4 * 2)
+        gs = p_gla.spec
+        us = timed(lambda: p_gla.mix(ctx, cache.views(4), projs["pg"], mids["pg"], 1.0))
+        out[f"pibulix_gated_linear_attention_{tag}"] = bytes_rec(us, rows * gs.num_heads * (3 * gs.head_dim + 2 * gs.v_head_dim) * 4 if pairs_full else
+                                                                 rows * gs.num_heads * gs.head_dim * gs.v_head_dim * 4 * 2)
+        a = torch.randn(rows, W, device=dev).to(bf)
+        ms, pm = moe.spec, p_moe.spec
+        us = timed(lambda: moe.forward(Ctx(), a))
+        pairs = rows * (ms.top + 1)
+        read = (min(ms.num_experts, rows * ms.top) + 1) * 3 * ms.expert_ff * W * 2
+        out[f"clamped_experts_{tag}"] = flops_rec(us, pairs * 6 * ms.expert_ff * W) if pairs_full else bytes_rec(us, read)
+        us = timed(lambda: p_moe.forward(Ctx(), a))
+        read = (min(pm.num_experts, rows * pm.top) + 1) * 3 * pm.expert_ff * W * 2
+        out[f"pibulix_experts_{tag}"] = flops_rec(us, rows * (pm.top + 1) * 6 * pm.expert_ff * W) if pairs_full else bytes_rec(us, read)
+        h = torch.randn(rows, W, device=dev)
+        o = torch.empty(rows, W, dtype=bf, device=dev)
+        us = timed(lambda: norm.add_forward(h, a, o))
+        out[f"norm_in_groups_{tag}"] = bytes_rec(us, rows * W * (4 + 4 + 2 + 2))
+        us = timed(lambda: p_norm.scale_add_forward(h, 1.0, a, o))
+        out[f"pibulix_norm_{tag}"] = bytes_rec(us, rows * W * (4 + 4 + 2 + 2))
+
+    entries = [diff.cache_requests(), par.cache_requests(), hg.cache_requests(), p_att.cache_requests(), p_gla.cache_requests()]
+    plans = list({p.key: p for part in (diff, par, p_att) for p in part.step_plans()}.values())
+    for tokens in (2048, 8192):
+        cache = Cache(entries, tokens + 64, 2, dev)
+        slot = cache.begin()
+        ctx = build_context(cache, [(slot, [0] * tokens, [])], dev, plans=plans)
+        fill(cache, 5)
+        steps(ctx, cache, tokens, str(tokens), tokens * (tokens + 1) // 2, sum(min(i + 1, window) for i in range(tokens)), 0, 0, 0)
+        cache.end(slot)
+        del cache
+    for batch in (8, 64):
+        context = 3000
+        cache = Cache(entries, batch * (context + 64), batch, dev)
+        slots = [cache.begin() for _ in range(batch)]
+        for sl in slots:
+            cache.reserve(sl, context + 1)
+            cache.length[sl] = context
+        ctx = build_context(cache, [(sl, [0], []) for sl in slots], dev, plans=plans)
+        fill(cache, 5)
+        steps(ctx, cache, batch, f"decode_b{batch}", 0, 0, context + 1, min(window, context + 1), min(ps.window, context + 1) + ps.keep_first)
+        del cache
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_design(args):
-    """``--design nilivik`` / ``--design pibulix`` / ``--design venidra``: prefill and decode of that decoder at Qwen3 layer sizes (random weights,
+    """``--design nilivik`` / ``--design pibulix`` / ``--design venidra`` / ``--design nevotar``: prefill and decode of that decoder at Qwen3 layer sizes (random weights,
     ``--layers`` layers, default 4) beside Qwen3 itself at the same width, layer count and parameters a
     layer, and the design's mixer kernels alone beside Qwen3's attention kernels. One JSON line."""
     import torch
@@ -810,11 +968,18 @@ def run_design(args):
     layers = args.layers or 4
     chunk = 2048
     vocab = 32768
-    out = {"design": args.design, "beside": "Qwen3ForCausalLM", "layers": layers, "chunk": chunk, "vocab": vocab, "dtype": "bf16",
+    out = {"design": args.design, "beside": "Pibulix" if args.design == "nevotar" else "Qwen3ForCausalLM", "layers": layers, "chunk": chunk, "vocab": vocab, "dtype": "bf16",
            "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
     for size in args.design_sizes.split(","):
         q = dict(SIZES[size]["config"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True)
-        if args.design == "venidra":
+        beside = ("qwen3", q)
+        if args.design == "nevotar":
+            n = nevotar_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers, vocab)
+            beside = ("pibulix", pibulix_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"],
+                                                layers, vocab, PIBULIX_WINDOW))
+            rec = {"width": q["hidden_size"], "window": NEVOTAR_WINDOW, "expert_ff": n["layers"][0]["mlp"]["expert"]["ff"],
+                   "beside": "Pibulix of the same width, layer count and feed-forward arithmetic (the closest of the library's designs)"}
+        elif args.design == "venidra":
             n = venidra_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers, vocab)
             rec = {"width": q["hidden_size"], "chunk": VENIDRA_CHUNK, "window": VENIDRA_WINDOW, "q_rank": n["layers"][1]["mixer"]["q_rank"],
                    "kv_rank": 512, "rot_dim": 64}
@@ -826,7 +991,7 @@ def run_design(args):
             n = nilivik_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers,
                                vocab, chunk)
             rec = {"width": q["hidden_size"], "nilivik_ff": n["layers"][0]["mlp"]["ff"]}
-        for name, cfg_d in ((args.design, n), ("qwen3", q)):
+        for name, cfg_d in ((args.design, n), beside):
             model = dk.random_model(dk.config_from_dict(cfg_d), seed=0, dtype=torch.bfloat16)
             r = {"weight_mb_per_step": round(model.weight_bytes_per_step() / 1e6, 1), "prefill": {}, "decode": {}}
             for tokens in (2048, 8192):
@@ -840,7 +1005,9 @@ def run_design(args):
             rec[name] = r
             del model
             torch.cuda.empty_cache()
-        if args.design == "venidra":
+        if args.design == "nevotar":
+            rec["kernels"] = nevotar_kernel_times(torch, dk, pk, n, beside[1])
+        elif args.design == "venidra":
             rec["kernels"] = venidra_kernel_times(torch, dk, pk, n, q["num_attention_heads"], q["num_key_value_heads"])
         elif args.design == "pibulix":
             rec["kernels"] = pibulix_kernel_times(torch, dk, pk, q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"],
@@ -1053,9 +1220,10 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --prefill-only: a prompt of another length")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
-    ap.add_argument("--design", default=None, choices=["nilivik", "pibulix", "venidra"],
+    ap.add_argument("--design", default=None, choices=["nilivik", "pibulix", "venidra", "nevotar"],
                     help="instead of the default workload: prefill and decode of this design at Qwen3 layer sizes beside Qwen3 "
-                         "itself at equal size, and its mixer kernels alone (one JSON line of its own)")
+                         "itself at equal size (nevotar: beside Pibulix, the closest of the library's designs), and its mixer "
+                         "kernels alone (one JSON line of its own)")
     ap.add_argument("--design-sizes", default="4b,8b", help="with --design: which of the layer sizes")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -1376,10 +1376,10 @@ def add_group_rmsnorm(h, delta, norm_w, eps, groups, a_out, rows=None):
 
 
 def gate_group_norm(o, x, skip, z, weight, eps, groups, out_scale, out):
-    """out = weight * grouped_rmsnorm((o + skip_h * x) * silu(z)) * out_scale: o and x float32 [T, n] with n = heads *
+    """out = weight * grouped_rmsnorm((o + skip_h * x) * silu(z)) * out_scale: o and x float32 [T, n] (x rows of a wider matrix) with n = heads *
     value size, ``skip`` float32 [heads] (None: no such term), the gate rows ``z`` and ``out`` in the storage type (rows
     of wider matrices), the norm over each of ``groups`` equal parts of the row."""
-    _need(o, "o", torch.float32, 2), _need(x, "x", torch.float32, 2), _need(skip, "skip", torch.float32, 1)
+    _need(o, "o", torch.float32, 2), _need_rows(x, "x", torch.float32), _need(skip, "skip", torch.float32, 1)
     _need(weight, "weight", torch.float32, 1), _need_rows(z, "z", out.dtype), _need_rows(out, "out")
     T, n = o.shape
     heads = skip.numel() if skip is not None else 1
@@ -1387,7 +1387,8 @@ def gate_group_norm(o, x, skip, z, weight, eps, groups, out_scale, out):
             or n % heads:
         raise KernelError("gate_group_norm: shapes do not match")
     lib = _lib("group_norm.cu")
-    _check(lib, lib.dk_gate_group_norm(_dt(out), _p(o), _p(x), _p(skip), n // heads, _p(z), c_longlong(z.stride(0)), _p(weight),
+    _check(lib, lib.dk_gate_group_norm(_dt(out), _p(o), _p(x), c_longlong(x.stride(0)), _p(skip), n // heads, _p(z), c_longlong(z.stride(0)),
+                                       _p(weight),
                                        c_float(eps), c_float(out_scale), _p(out), c_longlong(out.stride(0)), T, n, int(groups),
                                        _stream()), "gate_group_norm")
 
@@ -1404,68 +1405,82 @@ def diff_combine(a, lam, eps, out_scale, out, n_heads, v_head_dim):
 
 
 # ------------------------------------------------------------- recurrences over a float32 state, and what feeds them
+def recurrence_operands(rows, n_qk, n_v, device):
+    """One float32 matrix whose column ranges are the recurrence's q, k (n_qk wide) and v (n_v wide), so that the three
+    share a row stride, and the dense decays: -> (q, k, v, decay)."""
+    buf = torch.empty((rows, 2 * n_qk + n_v), dtype=torch.float32, device=device)
+    return buf[:, :n_qk], buf[:, n_qk:2 * n_qk], buf[:, 2 * n_qk:], torch.empty((rows, n_qk), dtype=torch.float32, device=device)
+
+
+def _need_operands(q, k, v, decay, what):
+    for t, nm in ((q, "q"), (k, "k"), (v, "v")):
+        _need_rows(t, nm, torch.float32)
+    _need(decay, "decay", torch.float32, 2)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or k.shape != q.shape or decay.shape != q.shape or v.shape[0] != q.shape[0]:
+        raise KernelError(f"{what}: q, k, v must be column ranges of one float32 matrix, the decays dense and as wide as q")
+
+
 def hgrn2_prepare(proj, f_bias, lower, q32, k32, a32, v32):
     """Rows [q | f | v] of a projection (n, n and nv wide) -> float32 q32 = silu(q), a32 = l + (1 - l) sigmoid(f + b),
-    k32 = 1 - a32, v32 = v."""
+    k32 = 1 - a32, v32 = v (operands from ``recurrence_operands``)."""
     _need_rows(proj, "proj"), _need(f_bias, "f_bias", torch.float32, 1), _need(lower, "lower", torch.float32, 1)
-    for t, nm in ((q32, "q32"), (k32, "k32"), (a32, "a32"), (v32, "v32")):
-        _need(t, nm, torch.float32, 2)
+    _need_operands(q32, k32, v32, a32, "hgrn2_prepare")
     T, n, nv = proj.shape[0], q32.shape[1], v32.shape[1]
-    if proj.shape[1] != 2 * n + nv or f_bias.numel() != n or lower.numel() != n or k32.shape != (T, n) or a32.shape != (T, n) or \
-            q32.shape[0] != T or v32.shape[0] != T:
+    if proj.shape[1] != 2 * n + nv or f_bias.numel() != n or lower.numel() != n or q32.shape[0] != T:
         raise KernelError("hgrn2_prepare: shapes do not match")
     lib = _lib("recurrence.cu")
     _check(lib, lib.dk_hgrn2_prepare(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(f_bias), _p(lower), _p(q32), _p(k32),
-                                     _p(a32), _p(v32), T, n, nv, _stream()), "hgrn2_prepare")
+                                     _p(a32), _p(v32), c_longlong(q32.stride(0)), T, n, nv, _stream()), "hgrn2_prepare")
 
 
-def ssd_prepare(xbc, dt, state, w_conv, conv_bias, taps, dt_bias, a_log, row_pos, row_seq, seq_pos0, seq_slot, x32, b32, c32,
-                dt32, a32):
-    """``xbc`` [T, C] and ``dt`` [T, heads]: columns of one projection (one row stride). [x32 | b32 | c32] = silu(conv(xbc) + bias)
-    with ``w_conv`` [C, taps] whose last column is the current token's and the sequence's ``state`` [slots, taps - 1, C]
-    for positions before the step (read only: ``conv_state_update`` moves it on); dt32 = softplus(dt + dt_bias);
-    a32 = exp(-exp(a_log) * dt32)."""
+def ssd_prepare(xbc, dt, state, w_conv, conv_bias, taps, dt_bias, a_log, row_pos, row_seq, seq_pos0, seq_slot, groups, q32, k32, a32, v32):
+    """``xbc`` [T, inner + 2 groups N] = [x | B | C] and ``dt`` [T, heads]: columns of one projection (one row stride).
+    y = silu(conv(xbc) + bias) with ``w_conv`` [C, taps] whose last column is the current token's and the sequence's
+    ``state`` [slots, taps - 1, C] for positions before the step (read only: ``conv_state_update`` moves it on);
+    dt <- softplus(dt + dt_bias). Out, head by head (head h of group g): q32 = C_g, k32 = dt_h B_g, a32 = exp(-exp(a_log_h)
+    dt_h) on every channel, v32 = x (operands from ``recurrence_operands``)."""
     _need_rows(xbc, "xbc"), _need_rows(dt, "dt", xbc.dtype), _need(state, "state", xbc.dtype, 3), _need(w_conv, "w_conv", xbc.dtype, 2)
     _need(conv_bias, "conv_bias", torch.float32, 1), _need(dt_bias, "dt_bias", torch.float32, 1), _need(a_log, "a_log", torch.float32, 1)
     for t, nm in ((row_pos, "row_pos"), (row_seq, "row_seq"), (seq_pos0, "seq_pos0"), (seq_slot, "seq_slot")):
         _need(t, nm, torch.int32, 1)
-    for t, nm in ((x32, "x32"), (b32, "b32"), (c32, "c32"), (dt32, "dt32"), (a32, "a32")):
-        _need(t, nm, torch.float32, 2)
+    _need_operands(q32, k32, v32, a32, "ssd_prepare")
     T, C = xbc.shape
-    nh = dt.shape[1]
-    inner, nbc = x32.shape[1], b32.shape[1]
+    nh, inner = dt.shape[1], v32.shape[1]
+    nbc = (C - inner) // 2
     if xbc.stride(0) != dt.stride(0) or tuple(w_conv.shape) != (C, taps) or not 1 <= taps <= SHORT_CONV_MAX_TAPS or \
             (taps > 1 and (state is None or tuple(state.shape[1:]) != (taps - 1, C))) or dt_bias.numel() != nh or a_log.numel() != nh or \
-            inner + 2 * nbc != C or x32.shape[0] != T or b32.shape != (T, nbc) or c32.shape != (T, nbc) or dt32.shape != (T, nh) or a32.shape != (T, nh) or (conv_bias is not None and conv_bias.numel() != C):
+            inner + 2 * nbc != C or groups < 1 or nh % groups or nbc % groups or q32.shape != (T, nh * (nbc // groups)) or \
+            (conv_bias is not None and conv_bias.numel() != C):
         raise KernelError("ssd_prepare: shapes do not match")
     lib = _lib("recurrence.cu")
     _check(lib, lib.dk_ssd_prepare(_dt(xbc), _p(xbc), _p(dt), c_longlong(xbc.stride(0)), _p(state), _p(w_conv), _p(conv_bias), int(taps),
-                                   _p(dt_bias), _p(a_log), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot), _p(x32), _p(b32), _p(c32), _p(dt32),
-                                   _p(a32), T, inner, nbc, nh, _stream()), "ssd_prepare")
+                                   _p(dt_bias), _p(a_log), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot), _p(q32), _p(k32),
+                                   _p(a32), _p(v32), c_longlong(q32.stride(0)), T, inner, nbc, nh, int(groups), _stream()), "ssd_prepare")
 
 
-def recurrence(q, k, k_factor, decay, v, out, state, cu_q, seq_pos0, seq_slot, n_seq, n_heads, head_dim, v_head_dim):
-    """S <- diag(decay_t) S + (k_factor_t k_t) v_t^T, o_t = S^T q_t per (sequence, head), token by token, all float32:
-    q, k [T, groups * head_dim] (head h reads group h / (n_heads / groups)), ``k_factor`` [T, n_heads] or None, ``decay``
-    [T, n_heads * head_dim] (per key channel) or [T, n_heads] (one number a head), v and out [T, n_heads * v_head_dim],
-    state [slots, n_heads, head_dim, v_head_dim]. Rows of sequence s are cu_q[s] .. cu_q[s + 1] (``cu_q`` None: row s
-    alone); seq_pos0[s] < 0 marks a padding row."""
-    for t, nm in ((q, "q"), (k, "k"), (k_factor, "k_factor"), (decay, "decay"), (v, "v"), (out, "out")):
-        _need(t, nm, torch.float32, 2)
-    _need(state, "state", torch.float32, 4)
+def recurrence(q, k, decay, v, out, state, cu_q, seq_pos0, seq_slot, n_seq, n_heads, head_dim, v_head_dim):
+    """S <- diag(decay_t) S + k_t v_t^T, o_t = S^T q_t per (sequence, head), token by token, all float32: q, k, decay
+    [T, n_heads * head_dim], v and out [T, n_heads * v_head_dim], state [slots, n_heads, head_dim, v_head_dim] (operands
+    from ``recurrence_operands``). Rows of sequence s are cu_q[s] .. cu_q[s + 1] (``cu_q`` None: row s alone);
+    seq_pos0[s] < 0 marks a padding row. Portions of key sizes 32, 64, 128 and 256 with value sizes in steps of 8 run on
+    the staged warp kernel of gated linear attention (rows ahead by cp.async), everything else (single tokens, other
+    sizes) on a kernel that keeps a warp's part of the state in registers and asks for the next token's rows a token ahead."""
+    _need_operands(q, k, v, decay, "recurrence")
+    _need(out, "out", torch.float32, 2), _need(state, "state", torch.float32, 4)
     _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
     T = q.shape[0]
-    if q.shape[1] % head_dim or k.shape != q.shape:
-        raise KernelError("recurrence: q and k must be [tokens, groups * head_dim]")
-    groups = q.shape[1] // head_dim
-    per_head = decay.shape[1] == n_heads and head_dim != 1
-    if groups < 1 or n_heads % groups or decay.shape not in ((T, n_heads), (T, n_heads * head_dim)) or \
-            v.shape != (T, n_heads * v_head_dim) or out.shape != v.shape or head_dim > 256 or \
-            tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or (k_factor is not None and k_factor.shape != (T, n_heads)):
+    if q.shape[1] != n_heads * head_dim or v.shape != (T, n_heads * v_head_dim) or out.shape != v.shape or head_dim > 256 or \
+            tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim):
         raise KernelError("recurrence: shapes do not match (key sizes up to 256)")
+    if cu_q is not None and gated_linear_attention_takes_warps(head_dim, v_head_dim):
+        lib = _lib("linear_attention.cu")
+        _check(lib, lib.dk_decayed_recurrence_warp(0, _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(decay), c_longlong(T), _p(out),
+                                                   _p(state), _p(cu_q), _p(seq_pos0), _p(seq_slot), n_seq, n_heads, head_dim,
+                                                   v_head_dim, _stream()), "recurrence")
+        return
     lib = _lib("recurrence.cu")
-    _check(lib, lib.dk_recurrence(_p(q), _p(k), groups, _p(k_factor), _p(decay), int(per_head), _p(v), _p(out), _p(state), _p(cu_q),
-                                  _p(seq_pos0), _p(seq_slot), n_seq, n_heads, head_dim, v_head_dim, _stream()), "recurrence")
+    _check(lib, lib.dk_recurrence(_p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(decay), _p(out), _p(state), _p(cu_q), _p(seq_pos0),
+                                  _p(seq_slot), n_seq, n_heads, head_dim, v_head_dim, _stream()), "recurrence")
 
 
 # ------------------------------------------------------------------ attention whose heads' scores are mixed

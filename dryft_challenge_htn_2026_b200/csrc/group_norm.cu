@@ -85,7 +85,7 @@ add_group_rmsnorm_kernel(float* h, const T* delta, const float* parts, int n_par
 
 template <typename T>
 __global__ void __launch_bounds__(GN_THREADS)
-gate_group_norm_kernel(const float* o, const float* x, const float* __restrict__ skip, int hdv, const T* z, long long ldz,
+gate_group_norm_kernel(const float* o, const float* x, long long ldx, const float* __restrict__ skip, int hdv, const T* z, long long ldz,
                        const float* __restrict__ w, float eps, float out_scale, T* out, long long ldo, int n, int groups) {
     extern __shared__ float gn_smem[];
     __shared__ float part_sums[GN_WARPS];
@@ -96,7 +96,7 @@ gate_group_norm_kernel(const float* o, const float* x, const float* __restrict__
     const size_t t = blockIdx.x;
     for (int i = threadIdx.x; i < n; i += GN_THREADS) {
         float v = o[t * n + i];
-        if (skip != nullptr) v = fmaf(skip[i / hdv], x[t * n + i], v);
+        if (skip != nullptr) v = fmaf(skip[i / hdv], x[t * ldx + i], v);
         const float g = to_f(z[t * ldz + i]);
         vals[i] = v * (g / (1.f + expf(-g)));
     }
@@ -152,7 +152,7 @@ DK_EXPORT int dk_add_group_rmsnorm(int dtype, float* h, const void* delta, const
                      n_parts, (size_t)part_stride, rows, w, eps, H, groups, (bf16*)a);
 }
 
-DK_EXPORT int dk_gate_group_norm(int dtype, const float* o, const float* x, const float* skip, int hdv, const void* z,
+DK_EXPORT int dk_gate_group_norm(int dtype, const float* o, const float* x, long long ldx, const float* skip, int hdv, const void* z,
                                  long long ldz, const float* w, float eps, float out_scale, void* out, long long ldo,
                                  int n_tok, int n, int groups, cudaStream_t st) {
     if (groups < 1 || n % groups || hdv < 1 || n % hdv) return (int)cudaErrorInvalidValue;
@@ -160,11 +160,11 @@ DK_EXPORT int dk_gate_group_norm(int dtype, const float* o, const float* x, cons
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (dtype == 0) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gate_group_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return dk_launch(gate_group_norm_kernel<float>, dim3(n_tok), dim3(GN_THREADS), smem, st, o, x, skip, hdv, (const float*)z,
+        return dk_launch(gate_group_norm_kernel<float>, dim3(n_tok), dim3(GN_THREADS), smem, st, o, x, ldx, skip, hdv, (const float*)z,
                          ldz, w, eps, out_scale, (float*)out, ldo, n, groups);
     }
     if (smem > 48 * 1024) cudaFuncSetAttribute(gate_group_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return dk_launch(gate_group_norm_kernel<bf16>, dim3(n_tok), dim3(GN_THREADS), smem, st, o, x, skip, hdv, (const bf16*)z, ldz, w,
+    return dk_launch(gate_group_norm_kernel<bf16>, dim3(n_tok), dim3(GN_THREADS), smem, st, o, x, ldx, skip, hdv, (const bf16*)z, ldz, w,
                      eps, out_scale, (bf16*)out, ldo, n, groups);
 }
 

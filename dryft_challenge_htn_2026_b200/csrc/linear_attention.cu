@@ -447,6 +447,21 @@ DK_EXPORT int dk_gated_linear_attention_warp(int dtype, const void* q, const voi
     return launch_gla_warp<bf16>(q, k, v, ld, z, out, state, cu_q, seq_pos0, seq_slot, n_seq, nh, hd, hdv, q_scale, vec, n_tok_max, st);
 }
 
+// The same recurrence with the decays given (float32 [rows, nh * hd]) instead of made from z: for mixers that make their
+// own decays, keys and queries (a forget gate with a lower bound, a state-space step). q, k, v of one row stride.
+DK_EXPORT int dk_decayed_recurrence_warp(int dtype, const void* q, const void* k, const void* v, long long ld, const float* decay,
+                                         long long n_rows, float* out, float* state, const int* cu_q, const int* seq_pos0,
+                                         const int* seq_slot, int n_seq, int nh, int hd, int hdv, cudaStream_t st) {
+    const long long n_tok_max = cu_q ? n_rows : 1;
+    if (hdv % 8 || hdv > 256 || (hd != 32 && hd != 64 && hd != 128 && hd != 256)) return (int)cudaErrorInvalidValue;
+    const int esz = dtype == 0 ? 4 : 2;
+    const int vec = ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay) % 16 == 0 && (ld * esz) % 16 == 0 &&
+                    (hd * esz) % 16 == 0 && (hdv * esz) % 16 == 0;
+    if (dtype == 0)
+        return launch_gla_warp<float>(q, k, v, ld, decay, out, state, cu_q, seq_pos0, seq_slot, n_seq, nh, hd, hdv, 1.f, vec, n_tok_max, st);
+    return launch_gla_warp<bf16>(q, k, v, ld, decay, out, state, cu_q, seq_pos0, seq_slot, n_seq, nh, hd, hdv, 1.f, vec, n_tok_max, st);
+}
+
 // out[t] = rmsnorm(o[t]) * w * sigmoid(gate[t]) * out_scale, the norm over each group of ``group`` columns of
 // the row (the whole row of all heads, width n, or one head at a time with a weight of the head's size,
 // shared by the heads); gate_act 1: SiLU of the gate instead of its sigmoid. Block (token, group).

@@ -64,12 +64,11 @@ class LowerBoundRecurrence(Part):
         if not writes:
             raise ValueError("a recurrent layer cannot read another layer's state")
         T = ctx.n_tok
-        q, k, a = (torch.empty((T, self.n_qk), dtype=torch.float32, device=dev) for _ in range(3))
-        v = torch.empty((T, self.n_mid), dtype=torch.float32, device=dev)
+        q, k, v, a = api.recurrence_operands(T, self.n_qk, self.n_mid, dev)
         api.hgrn2_prepare(proj[:, :self.n_in], self.f_bias, self.lower, q, k, a, v)
         o = torch.empty((T, self.n_mid), dtype=torch.float32, device=dev)
         cu_q, pos0, n_seq = _sequences(ctx)
-        api.recurrence(q, k, None, a, v, o, views[0].state, cu_q, pos0, ctx.seq_slot, n_seq, s.num_heads, s.head_dim, s.v_head_dim)
+        api.recurrence(q, k, a, v, o, views[0].state, cu_q, pos0, ctx.seq_slot, n_seq, s.num_heads, s.head_dim, s.v_head_dim)
         api.norm_gate(o, self.norm_weight, s.norm_eps, None, scale, mid, group=s.v_head_dim)
 
     def forward(self, ctx, views, a, writes=True):
@@ -135,18 +134,15 @@ class StateSpace(Part):
         xbc = proj[:, inner:inner + self.n_conv]
         dt = proj[:, inner + self.n_conv:self.n_in]
         conv_state = views[1].state if s.conv_taps > 1 else None
-        x = torch.empty((T, inner), dtype=torch.float32, device=dev)
-        b = torch.empty((T, nbc), dtype=torch.float32, device=dev)
-        c = torch.empty((T, nbc), dtype=torch.float32, device=dev)
-        dt32 = torch.empty((T, s.num_heads), dtype=torch.float32, device=dev)
-        a32 = torch.empty((T, s.num_heads), dtype=torch.float32, device=dev)
+        # the recurrence's operands head by head: q = C and k = dt B of the head's group, the head's decay on every channel
+        q, k, x, a = api.recurrence_operands(T, s.num_heads * s.state_dim, inner, dev)
         cu_q, pos0, n_seq = _sequences(ctx)
         api.ssd_prepare(xbc, dt, conv_state, self.w_conv, self.conv_bias, s.conv_taps, self.dt_bias, self.a_log, ctx.row_pos,
-                        ctx.row_seq, pos0, ctx.seq_slot, x, b, c, dt32, a32)
+                        ctx.row_seq, pos0, ctx.seq_slot, s.groups, q, k, a, x)
         if s.conv_taps > 1:
             api.conv_state_update(xbc, conv_state, s.conv_taps, cu_q, pos0, ctx.seq_slot, n_seq)
         y = torch.empty((T, inner), dtype=torch.float32, device=dev)
-        api.recurrence(c, b, dt32, a32, x, y, views[0].state, cu_q, pos0, ctx.seq_slot, n_seq, s.num_heads, s.state_dim, s.v_head_dim)
+        api.recurrence(q, k, a, x, y, views[0].state, cu_q, pos0, ctx.seq_slot, n_seq, s.num_heads, s.state_dim, s.v_head_dim)
         api.gate_group_norm(y, x, self.skip, z, self.norm_weight, s.norm_eps, s.norm_groups, scale, mid)
 
     def forward(self, ctx, views, a, writes=True):
