@@ -1521,7 +1521,7 @@ def talk_bf16_takes(n_heads, n_kv_heads, head_dim, v_head_dim):
     of 16 up to 256, and a run of 32 keys and values of every kv head beside the heads' score tiles in shared memory."""
     if head_dim % 16 or v_head_dim % 16 or max(head_dim, v_head_dim) > 256 or n_heads > TALK_MAX_HEADS:
         return False
-    smem = 2 * n_kv_heads * 32 * (head_dim + 8 + v_head_dim + 8) + 4 * (n_heads * 16 * 34 + n_heads * n_heads)
+    smem = 2 * n_kv_heads * 32 * (head_dim + 8 + v_head_dim + 8) + 4 * (n_heads * 16 * 40 + n_heads * n_heads)
     return smem <= _TALK_SMEM
 
 

@@ -18,7 +18,8 @@ static_assert(HD % 16 == 0 && HDV % 16 == 0 && HD <= 256 && HDV <= 256, "head si
 #define TK_KB 32                    // keys a run
 #define TK_ROWS 16                  // queries a block
 #define TK_MAX_WARPS 16
-constexpr int KSTR = HD + 8, VSTR = HDV + 8, SSTR = TK_KB + 2;
+// rows of scores 40 floats apart: the 16 lanes of a half warp (4 rows x 4 pairs of columns) then read 16 different pairs of banks
+constexpr int KSTR = HD + 8, VSTR = HDV + 8, SSTR = TK_KB + 8;
 
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(

@@ -51,11 +51,28 @@ __device__ __forceinline__ void group_scales(F value, int n, int groups, float e
     __syncthreads();
 }
 
-template <typename T>
+__device__ __forceinline__ float4 gn_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 gn_ld4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void gn_st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void gn_st4(bf16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+
+// VEC: four columns a thread at a time (the row's and a part's size are multiples of 4, rows on 16-byte boundaries)
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(GN_THREADS)
 add_group_rmsnorm_kernel(float* h, const T* delta, const float* parts, int n_parts, size_t part_stride, const int* rows,
                          const float* __restrict__ w, float eps, int H, int groups, T* a) {
-    extern __shared__ float gn_smem[];       // [H] the row as it stands after the sum, then [groups] scales
+    extern __shared__ __align__(16) float gn_smem[];       // [H] the row as it stands after the sum, then [groups] scales
     __shared__ float part_sums[GN_WARPS];
     float* vals = gn_smem;
     float* scales = gn_smem + H;
@@ -65,22 +82,50 @@ add_group_rmsnorm_kernel(float* h, const T* delta, const float* parts, int n_par
     const size_t row = rows ? (size_t)rows[out_row] : out_row;
     float* hr = h + row * H;
     const T* dr = delta ? delta + row * H : nullptr;
-    for (int i = threadIdx.x; i < H; i += GN_THREADS) {
-        float v = hr[i];
-        if (dr) v += to_f(dr[i]);
-        if (parts) {
-            float d = 0.f;
-            for (int k = 0; k < n_parts; k++) d += parts[(size_t)k * part_stride + row * H + i];
-            v += d;
+    if (VEC) {
+        for (int i = 4 * threadIdx.x; i < H; i += 4 * GN_THREADS) {
+            float4 v = gn_ld4(hr + i);
+            if (dr) {
+                const float4 d = gn_ld4(dr + i);
+                v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+            }
+            if (parts) {
+                float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int k = 0; k < n_parts; k++) {
+                    const float4 u = gn_ld4(parts + (size_t)k * part_stride + row * H + i);
+                    d.x += u.x, d.y += u.y, d.z += u.z, d.w += u.w;
+                }
+                v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+            }
+            gn_st4(vals + i, v);
+            if (!rows && (dr || parts)) gn_st4(hr + i, v);
         }
-        vals[i] = v;
-        if (!rows && (dr || parts)) hr[i] = v;
+    } else {
+        for (int i = threadIdx.x; i < H; i += GN_THREADS) {
+            float v = hr[i];
+            if (dr) v += to_f(dr[i]);
+            if (parts) {
+                float d = 0.f;
+                for (int k = 0; k < n_parts; k++) d += parts[(size_t)k * part_stride + row * H + i];
+                v += d;
+            }
+            vals[i] = v;
+            if (!rows && (dr || parts)) hr[i] = v;
+        }
     }
     __syncthreads();
     group_scales([&](int i) { return vals[i]; }, H, groups, eps, part_sums, scales);
     const int gs = H / groups;
     T* ar = a + out_row * H;
-    for (int i = threadIdx.x; i < H; i += GN_THREADS) ar[i] = from_f<T>(vals[i] * scales[i / gs] * w[i]);
+    if (VEC) {
+        for (int i = 4 * threadIdx.x; i < H; i += 4 * GN_THREADS) {
+            const float4 v = gn_ld4(vals + i), ww = gn_ld4(w + i);
+            const float sc = scales[i / gs];
+            gn_st4(ar + i, make_float4(v.x * sc * ww.x, v.y * sc * ww.y, v.z * sc * ww.z, v.w * sc * ww.w));
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += GN_THREADS) ar[i] = from_f<T>(vals[i] * scales[i / gs] * w[i]);
+    }
 }
 
 template <typename T>
@@ -142,14 +187,21 @@ DK_EXPORT int dk_add_group_rmsnorm(int dtype, float* h, const void* delta, const
     if (groups < 1 || H % groups) return (int)cudaErrorInvalidValue;
     const size_t smem = sizeof(float) * (size_t)(H + groups);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    if (dtype == 0) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(add_group_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return dk_launch(add_group_rmsnorm_kernel<float>, dim3(n_rows), dim3(GN_THREADS), smem, st, h, (const float*)delta, parts,
-                         n_parts, (size_t)part_stride, rows, w, eps, H, groups, (float*)a);
+    const bool vec = H % 4 == 0 && (H / groups) % 4 == 0 && part_stride % 4 == 0 &&
+                     ((uintptr_t)h | (uintptr_t)delta | (uintptr_t)parts | (uintptr_t)w | (uintptr_t)a) % 16 == 0;
+#define GN_LAUNCH(T, V)                                                                                                       \
+    {                                                                                                                         \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_group_rmsnorm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return dk_launch(add_group_rmsnorm_kernel<T, V>, dim3(n_rows), dim3(GN_THREADS), smem, st, h, (const T*)delta, parts, n_parts, \
+                         (size_t)part_stride, rows, w, eps, H, groups, (T*)a);                                                \
     }
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_group_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return dk_launch(add_group_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(GN_THREADS), smem, st, h, (const bf16*)delta, parts,
-                     n_parts, (size_t)part_stride, rows, w, eps, H, groups, (bf16*)a);
+    if (dtype == 0) {
+        if (vec) GN_LAUNCH(float, true)
+        GN_LAUNCH(float, false)
+    }
+    if (vec) GN_LAUNCH(bf16, true)
+    GN_LAUNCH(bf16, false)
+#undef GN_LAUNCH
 }
 
 DK_EXPORT int dk_gate_group_norm(int dtype, const float* o, const float* x, long long ldx, const float* skip, int hdv, const void* z,
