@@ -46,15 +46,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // tiles (prompts): tiles[2i] = sequence, tiles[2i + 1] = first query of the tile within the sequence's rows of this step.
 // tiles == nullptr (single tokens): block x is row x, its position row_pos[x], its page table row x.
+template <bool QS>
 __global__ void __launch_bounds__(32 * TK_MAX_WARPS)
 attn_talk_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, float out_scale, const bf16* k_store, const bf16* v_store,
                  const int* tiles, const int* cu_q, const int* seq_pos0, const int* row_pos, const int* page_table, int pt_stride,
                  int nh, int nkv, int window, float scale, const float* __restrict__ talk, int nsplit, float* ws_acc, float* ws_ml) {
+    constexpr bool q_staged = QS;
     extern __shared__ __align__(16) unsigned char tk_smem[];
     bf16* Ks = reinterpret_cast<bf16*>(tk_smem);                                   // [nkv][TK_KB][KSTR]
     bf16* Vs = Ks + (size_t)nkv * TK_KB * KSTR;                                    // [nkv][TK_KB][VSTR]
     float* S = reinterpret_cast<float*>(Vs + (size_t)nkv * TK_KB * VSTR);          // [nh][TK_ROWS][SSTR]
     float* Tm = S + (size_t)nh * TK_ROWS * SSTR;                                   // [nh][nh] talk * scale * log2(e)
+    bf16* Qs = reinterpret_cast<bf16*>(Tm + (((size_t)nh * nh + 3) & ~(size_t)3));  // [nh][TK_ROWS][KSTR], when q_staged
     pdl_wait();
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, t4 = lane & 3;
@@ -100,6 +103,16 @@ attn_talk_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, float o
     const int run0 = run_first + blockIdx.y * per, run1 = min(run_end, run0 + per);
     const bf16* qrow[2] = {gq < rows_here ? q + (size_t)(row_first + gq) * ldq : nullptr,
                            gq + 8 < rows_here ? q + (size_t)(row_first + gq + 8) * ldq : nullptr};
+    if (q_staged) {      // the tile's query rows of every head into shared memory once (zeros for rows past the end): read by ldmatrix in every run
+        constexpr int QP = HD / 8;
+        for (int i = tid; i < nh * TK_ROWS * QP; i += blockDim.x) {
+            const int pc = i % QP, rr = (i / QP) % TK_ROWS, g = i / (QP * TK_ROWS);
+            bf16* dst = Qs + ((size_t)g * TK_ROWS + rr) * KSTR + pc * 8;
+            if (rr < rows_here) cp_async16(dst, q + (size_t)(row_first + rr) * ldq + (size_t)g * HD + pc * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");     // waited for with the first run's keys
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float acc[HDV / 8][4];
 #pragma unroll
@@ -131,10 +144,14 @@ attn_talk_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, float o
             for (int ks = 0; ks < HD / 16; ks++) {
                 const int c = g * HD + ks * 16 + 2 * t4;
                 uint32_t a[4];
-                a[0] = qrow[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + c) : 0u;
-                a[1] = qrow[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + c) : 0u;
-                a[2] = qrow[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + c + 8) : 0u;
-                a[3] = qrow[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + c + 8) : 0u;
+                if (q_staged) {
+                    ldsm_x4(a, Qs + ((size_t)g * TK_ROWS + (lane & 15)) * KSTR + ks * 16 + 8 * (lane >> 4));
+                } else {
+                    a[0] = qrow[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + c) : 0u;
+                    a[1] = qrow[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + c) : 0u;
+                    a[2] = qrow[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + c + 8) : 0u;
+                    a[3] = qrow[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + c + 8) : 0u;
+                }
 #pragma unroll
                 for (int np = 0; np < TK_KB / 16; np++) {
                     uint32_t b[4];
@@ -280,11 +297,10 @@ __global__ void attn_talk_merge_kernel(const float* ws_acc, const float* ws_ml, 
     }
 }
 
-static size_t talk_smem(int nh, int nkv) {
-    return sizeof(bf16) * (size_t)nkv * TK_KB * (KSTR + VSTR) + sizeof(float) * ((size_t)nh * TK_ROWS * SSTR + (size_t)nh * nh);
+static size_t talk_smem(int nh, int nkv, bool q_staged) {
+    return sizeof(bf16) * (size_t)nkv * TK_KB * (KSTR + VSTR) + sizeof(float) * ((size_t)nh * TK_ROWS * SSTR + (((size_t)nh * nh + 3) & ~(size_t)3)) +
+           (q_staged ? sizeof(bf16) * (size_t)nh * TK_ROWS * KSTR : 0);
 }
-
-DK_EXPORT int dk_attention_talk_smem(int nh, int nkv) { return (int)talk_smem(nh, nkv); }
 
 // n_tiles blocks of 16 queries (tiles) or n_tiles single tokens (tiles == nullptr, keys in nsplit runs with the merge)
 DK_EXPORT int dk_attention_talk_bf16(const void* q, long long ldq, void* out, long long ldo, float out_scale, const void* k_store,
@@ -293,19 +309,25 @@ DK_EXPORT int dk_attention_talk_bf16(const void* q, long long ldq, void* out, lo
                                      float scale, const float* talk, int nsplit, float* ws_acc, float* ws_ml, cudaStream_t st) {
     if (nh < 1 || nh > 64 || nkv < 1 || nh % nkv || nsplit < 1 || (nsplit > 1 && (tiles != nullptr || ws_acc == nullptr || ws_ml == nullptr)))
         return (int)cudaErrorInvalidValue;
-    const size_t smem = talk_smem(nh, nkv);
+    // the query rows stay in shared memory where there is room (16-byte rows), else every run reads them from memory again
+    const bool q_staged = talk_smem(nh, nkv, true) <= 220 * 1024 && (uintptr_t)q % 16 == 0 && (ldq * 2) % 16 == 0;
+    const size_t smem = talk_smem(nh, nkv, q_staged);
     if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
-    static size_t attr = 0;
-    if (smem > 48 * 1024 && smem > attr) {
-        cudaError_t e = cudaFuncSetAttribute(attn_talk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t attr[2] = {0, 0};
+    if (smem > 48 * 1024 && smem > attr[q_staged]) {
+        cudaError_t e = q_staged ? cudaFuncSetAttribute(attn_talk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                 : cudaFuncSetAttribute(attn_talk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        attr = smem;
+        attr[q_staged] = smem;
     }
     const int warps = nh < TK_MAX_WARPS ? nh : TK_MAX_WARPS;
     const dim3 grid(n_tiles, nsplit, (nh + warps - 1) / warps), block(32 * warps);
-    int e = dk_launch(attn_talk_kernel, grid, block, smem, st, (const bf16*)q, ldq, (bf16*)out, ldo, out_scale, (const bf16*)k_store,
-                      (const bf16*)v_store, tiles, cu_q, seq_pos0, row_pos, page_table, pt_stride, nh, nkv, window, scale, talk, nsplit,
-                      ws_acc, ws_ml);
+    int e = q_staged ? dk_launch(attn_talk_kernel<true>, grid, block, smem, st, (const bf16*)q, ldq, (bf16*)out, ldo, out_scale,
+                                 (const bf16*)k_store, (const bf16*)v_store, tiles, cu_q, seq_pos0, row_pos, page_table, pt_stride, nh,
+                                 nkv, window, scale, talk, nsplit, ws_acc, ws_ml)
+                     : dk_launch(attn_talk_kernel<false>, grid, block, smem, st, (const bf16*)q, ldq, (bf16*)out, ldo, out_scale,
+                                 (const bf16*)k_store, (const bf16*)v_store, tiles, cu_q, seq_pos0, row_pos, page_table, pt_stride, nh,
+                                 nkv, window, scale, talk, nsplit, ws_acc, ws_ml);
     if (e || nsplit == 1) return e;
     const int warps_m = n_tiles * nh;
     return dk_launch(attn_talk_merge_kernel, dim3((warps_m + 3) / 4), dim3(128), 0, st, (const float*)ws_acc, (const float*)ws_ml,
