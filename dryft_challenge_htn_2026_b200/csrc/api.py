@@ -1531,12 +1531,19 @@ def talk_operands(q, out):
 
 
 def talk_decode_splits(rows, n_heads, table_pages, window):
-    """Runs of keys a single-token step of attention_talk_bf16 deals out over blocks: enough blocks for the GPU, no more
-    than there are runs of 32 keys in sight; a function of the step's shape alone (a captured graph keeps it)."""
+    """Runs of keys a single-token step of attention_talk_bf16 deals out over blocks (one block an SM at a time): the count
+    that makes waves of blocks times runs a block smallest, no more than there are runs of 32 keys in sight; a function of
+    the step's shape alone (a captured graph keeps it)."""
     keys = table_pages * PAGE if not window else min(window + 32, table_pages * PAGE)
     runs = max(1, (keys + 31) // 32)
     blocks = rows * ((n_heads + 15) // 16)
-    return max(1, min(TALK_MAX_SPLITS, runs, (2 * sm_count() + blocks - 1) // blocks))
+    sms = sm_count()
+    best, best_cost = 1, None
+    for ns in range(1, min(TALK_MAX_SPLITS, runs) + 1):
+        cost = -(-blocks * ns // sms) * (-(-runs // ns) + 0.5)       # a block's start and its part of the merge count as half a run
+        if best_cost is None or cost < best_cost:
+            best, best_cost = ns, cost
+    return best
 
 
 def talk_decode_ws(rows, n_heads, v_head_dim, nsplit, device):

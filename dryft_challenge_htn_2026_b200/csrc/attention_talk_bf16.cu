@@ -173,7 +173,7 @@ attn_talk_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, float o
         float x[TK_KB / 8][4];
 #pragma unroll
         for (int i = 0; i < TK_KB / 8; i++) x[i][0] = x[i][1] = x[i][2] = x[i][3] = 0.f;
-        for (int g = 0; g < nh; g++) {
+        for (int g = 0; g < nh && (hi[0] >= 0 || hi[1] >= 0); g++) {      // rows that do not exist (a single token has one) are masked anyway
             const float tg = Tm[h * nh + g];
             const float* Sg = S + (size_t)g * TK_ROWS * SSTR;
 #pragma unroll
@@ -310,7 +310,8 @@ DK_EXPORT int dk_attention_talk_bf16(const void* q, long long ldq, void* out, lo
     if (nh < 1 || nh > 64 || nkv < 1 || nh % nkv || nsplit < 1 || (nsplit > 1 && (tiles != nullptr || ws_acc == nullptr || ws_ml == nullptr)))
         return (int)cudaErrorInvalidValue;
     // the query rows stay in shared memory where there is room (16-byte rows), else every run reads them from memory again
-    const bool q_staged = talk_smem(nh, nkv, true) <= 220 * 1024 && (uintptr_t)q % 16 == 0 && (ldq * 2) % 16 == 0;
+    // (a single token has one row: it is read from memory, and two blocks may share an SM)
+    const bool q_staged = tiles != nullptr && talk_smem(nh, nkv, true) <= 220 * 1024 && (uintptr_t)q % 16 == 0 && (ldq * 2) % 16 == 0;
     const size_t smem = talk_smem(nh, nkv, q_staged);
     if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
     static size_t attr[2] = {0, 0};
