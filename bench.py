@@ -801,21 +801,21 @@ NEVOTAR_WINDOW = 1024
 
 def nevotar_config(width, heads, kv_heads, ff_qwen, layers, vocab):
     """A Nevotar model of Qwen3's width, layer count and feed-forward arithmetic: differential attention of half Qwen3's
-    head counts (two maps of 64 side by side, values of 128, a temperature every 64 positions), an HGRN2 layer of as many
+    head counts (two maps of 64 side by side, values of 128, a temperature every 128 positions), an HGRN2 layer of as many
     heads of 128, and layers that run attention with mixed head scores (heads of 128, half the head rotated, a window of
     1,024) beside a state-space mixer as wide as the model (heads of 128, states of 128, 4 groups, 4 taps); every layer
     with a mixture of 32 clamped experts of which a token uses 4, each a quarter of Qwen3's feed-forward, and a shared one."""
     h2, g2 = heads // 2, max(1, kv_heads // 2)
     eff = max(64, ff_qwen // 4 // 64 * 64)
     mlp = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": 32, "top": 4}, "shared": {"ff": eff, "limit": 7.0}}
-    att = {"type": "attention", "mixer": {"heads": h2, "kv_heads": g2, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.6,
-                                          "q_temp": {"coef": 0.5, "every": 64}}, "mlp": mlp}
+    att = {"type": "attention", "mixer": {"heads": h2, "kv_heads": g2, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.5,
+                                          "q_temp": {"coef": 0.25, "every": 128}}, "mlp": mlp}
     hg = {"type": "hgrn2", "mixer": {"heads": h2, "dim": 128, "vdim": 128}, "mlp": mlp}
     par = {"type": "parallel",
-           "mixer": {"left": {"heads": h2, "kv_heads": g2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 1e6},
+           "mixer": {"left": {"heads": h2, "kv_heads": g2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 5e5},
                               "mask": {"size": NEVOTAR_WINDOW}},
                      "right": {"heads": width // 128, "vdim": 128, "state": 128, "groups": 4, "conv": 4, "norm_groups": 4},
-                     "left_scale": 0.6, "right_scale": 0.9}, "mlp": mlp}
+                     "left_scale": 0.7, "right_scale": 0.8}, "mlp": mlp}
     return dict(architecture="Nevotar", vocab=vocab, width=width, norm={"eps": 1e-6, "groups": 2},
                 layers=[(att, hg, par, par)[i % 4] for i in range(layers)])
 

@@ -78,9 +78,9 @@ SHAPES = {
     # head sizes the tensor-core kernels are built for (two maps of 32 and of 64 side by side), a window that spans pages
     # and none, wide states, a norm in 2 groups
     "C": dict(architecture="Nevotar", vocab=320, width=128, norm={"eps": 1e-6, "groups": 2},
-              layers=[att(2, 1, 32, 64, 0.17, 0.6, (0.5, 40), moe(8, 64, 2.5, 2, (64, 2.0))),
+              layers=[att(2, 1, 32, 64, 0.17, 0.55, (0.5, 40), moe(8, 64, 2.5, 2, (64, 2.0))),
                       par((8, 4, 64, 32, 0.125, (64, 250000.0), 100), (4, 64, 128, 2, 4, 1), 0.75, 0.8, moe(8, 64, 2.5, 2, (64, 2.0))),
-                      att(2, 2, 64, 128, 0.11, 0.4, (1.0, 64), None),
+                      att(2, 2, 64, 128, 0.11, 0.4, (1.0, 72), None),
                       par((2, 1, 128, 128, 0.09, (32, 10000.0), None), (2, 32, 64, 1, 3, 2), 1.5, 0.5, moe(4, 32, 1.0, 2, None))]),
     # sizes that no tensor-core kernel takes: heads of 10 / 20 / 24, values of 10 (no multiple of 4), an expert size of
     # 20, three state-space groups, a norm of the width in 3 groups and of the inner size in 5, a convolution of one tap
@@ -192,7 +192,7 @@ def test_a_tiny_row_shows_eps_inside_the_root_of_each_group():
     assert float(out[0, :4].abs().max()) < 0.5          # the small group is held down by eps, not blown up to unit size
 
 
-DIFF_SHAPES = [(4, 2, 16, 16, (0.3, 5)), (3, 3, 16, 32, None), (2, 1, 32, 64, (0.5, 40)), (3, 1, 10, 20, (2.0, 3)), (2, 2, 64, 128, (1.0, 64)),
+DIFF_SHAPES = [(4, 2, 16, 16, (0.3, 5)), (3, 3, 16, 32, None), (2, 1, 32, 64, (0.5, 40)), (3, 1, 10, 20, (2.0, 3)), (2, 2, 64, 128, (1.0, 72)),
                (1, 1, 24, 8, (0.7, 1))]
 
 
