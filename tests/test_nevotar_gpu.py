@@ -532,6 +532,99 @@ def test_long_decoding_through_the_decode_state_and_its_graph(tmp_path, name, dt
     api.gemm_tc_check()
 
 
+def random_config(rng):
+    """A configuration drawn at random: any order of layers, shared weights, sizes that no kernel was built for."""
+    width = rng.choice([40, 48, 60, 100, 128, 160])
+    groups = rng.choice([g for g in (1, 2, 4, 5, 8) if width % g == 0])
+
+    def mlp():
+        if rng.random() < 0.15:
+            return None
+        E = rng.choice([2, 3, 4, 8, 16])
+        return moe(E, rng.choice([8, 20, 32, 64]), rng.choice([0.5, 2.0, 7.0]), rng.randint(1, min(E, 4)),
+                   (rng.choice([8, 24, 32]), rng.choice([1.0, 7.0])) if rng.random() < 0.7 else None)
+
+    def heads():
+        G = rng.choice([1, 2, 3, 4])
+        return G * rng.choice([1, 2, 3, 4]), G
+
+    def one():
+        kind = rng.choice(["attention", "hgrn2", "parallel"])
+        if kind == "attention":
+            H, G = heads()
+            D = rng.choice([8, 12, 16, 24, 32, 64])
+            return att(H, G, D, rng.choice([8, 16, 20, 32, 64, 128]), D ** -0.5 * rng.choice([0.5, 1.0, 2.0]), rng.choice([0.2, 0.5, 0.8]),
+                       (rng.choice([0.1, 0.5, 1.0]), rng.choice([1, 3, 16, 100])) if rng.random() < 0.8 else None, mlp())
+        if kind == "hgrn2":
+            return hg(rng.choice([1, 2, 3, 4, 6]), rng.choice([8, 16, 24, 32, 64, 128]), rng.choice([6, 8, 16, 32, 40]), mlp())
+        H, G = heads()
+        D = rng.choice([8, 16, 20, 32, 64, 128])
+        rot = (rng.choice([d for d in (2, 4, 8, 16, 32, 64, 128) if d <= D]), rng.choice([100.0, 1e4, 1e6])) if rng.random() < 0.8 else None
+        g = rng.choice([1, 2, 3, 4])
+        rh, rv = g * rng.choice([1, 2, 3]), rng.choice([4, 8, 12, 16, 32, 64])
+        right = (rh, rv, rng.choice([8, 16, 24, 32, 64, 128]), g, rng.choice([1, 2, 3, 4]), rng.choice([n for n in (1, 2, 3, 4, 6) if (rh * rv) % n == 0]))
+        return par((H, G, D, rng.choice([8, 12, 16, 32, 64]), D ** -0.5, rot, rng.choice([None, 1, 2, 7, 31, 32, 33, 64, 65, 100, 128])),
+                   right, rng.choice([0.5, 1.0]), rng.choice([0.8, 1.5]), mlp())
+
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        if layers and rng.random() < 0.3:
+            j = rng.choice([k for k, l in enumerate(layers) if "weights_of" not in l])
+            layers.append(dict(json.loads(json.dumps(layers[j])), weights_of=j))
+        else:
+            layers.append(one())
+    return dict(architecture="Nevotar", vocab=rng.choice([50, 136, 333]), width=width, norm={"eps": rng.choice([1e-6, 1e-5]), "groups": groups},
+                layers=layers)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_through_batches_the_decode_state_and_portions(tmp_path, seed):
+    import random
+
+    from safetensors.torch import load_file, save_file
+
+    cfg = dk.config_from_dict(random_config(random.Random(1000 + seed)))
+    folder = str(tmp_path / "model")
+    dk.write_random_model(cfg, folder, seed=seed, dtype=torch.float32, matrix_std=0.08)
+    # the random-weights mode spreads routers wide: scores that reach 1 in float32 would tie, which float64 does not
+    path = os.path.join(folder, "model.safetensors")
+    save_file({k: (v * 0.15 if k.endswith(".router") else v).contiguous() for k, v in load_file(path).items()}, path)
+    lens = [1, 37, 150, 230]
+    seqs = [random_tokens(cfg.vocab, n, 10 * seed + i) for i, n in enumerate(lens)]
+    ref = [plain_logits(folder, s) for s in seqs]
+    for dtype in DTYPES:
+        runner = Runner(load_model(folder, dtype), 64 * 24, 6)
+        errs = Errors(dtype)
+
+        def check(out, pairs, what):
+            out = out.cpu().double()
+            for row, (i, p) in enumerate(pairs):
+                errs.add(float((out[row] - ref[i][p]).abs().max()), tol(dtype, ref[i]), f"seed {seed} {what}: sequence {i} position {p}")
+
+        for use_graph in (False, True):
+            cut = [1, 20, 100, 140]
+            slots = [runner.begin() for _ in seqs]
+            check(runner.step([(sl, s[:c], [c - 1]) for sl, s, c in zip(slots, seqs, cut)]), [(i, c - 1) for i, c in enumerate(cut)], "prompts")
+            loop = DecodeLoop(runner, use_graph=use_graph)
+            live, k = [i for i in range(4) if cut[i] < lens[i]], 0
+            while live and k < 40:
+                check(loop.forced_step([(slots[i], [seqs[i][cut[i] + k]], [0]) for i in live]), [(i, cut[i] + k) for i in live], f"token {k}")
+                k += 1
+                for i in [i for i in live if cut[i] + k >= lens[i]]:
+                    runner.end(slots[i])
+                    slots[i] = None
+                live = [i for i in live if cut[i] + k < lens[i]]
+            for sl in slots:
+                if sl is not None:
+                    runner.end(sl)
+        slot, at = runner.begin(), 0
+        for n in [64, 2, 31, 1, 2, 70, 30]:
+            check(runner.step([(slot, seqs[3][at:at + n], [0, n - 1])]), [(3, at), (3, at + n - 1)], f"portion of {n} at {at}")
+            at += n
+        runner.end(slot)
+        errs.verdict()
+
+
 @pytest.mark.parametrize("name", ["A", "D"])
 def test_greedy_generation_through_the_entry_point(tmp_path, name):
     folder, cfg = make_model(tmp_path, name, seed=5)
