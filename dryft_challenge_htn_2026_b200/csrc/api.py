@@ -309,6 +309,12 @@ MODE_STORE, MODE_STORE_F32, MODE_SILU, MODE_XIELU = 0, 1, 2, 3
 GATE_GELU = (1.0, 0.0)      # ``act`` of a MODE_SILU product whose gate goes through the tanh form of GELU instead of SiLU
 
 
+def gate_clamped(limit):
+    """``act`` of a MODE_SILU product with the clamped gate: g' = min(g, limit), u' = clamp(u, -limit, limit),
+    out = g' sigmoid(1.702 g') (u' + 1)."""
+    return (2.0, float(limit))
+
+
 def sgemm(x, w, out, mode=MODE_STORE, act=(0.0, 0.0)):
     """float32 out = x . w^T on CUDA cores; mode MODE_SILU: w = [gate; up], out = silu(g) * u; mode MODE_XIELU:
     out = xielu(x . w^T) with the constants ``act`` = (alpha_pos, alpha_neg)."""
@@ -474,8 +480,8 @@ def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None, act=(0.0, 0.0)):
     lib = _lib("gemm_tc.cu")
     _check(lib, lib.dk_gemm_tc(_p(x), _p(w), _p(None if ws is not None else out), M, N, K,
                                MODE_STORE if mode == MODE_STORE_F32 else mode, _p(_tc_err), sk, _p(ws), bn,
-                               2 if (mode == MODE_SILU and act[0] > 0.5) else int(xielu),
-                               c_float(act[0]), c_float(act[1]), _stream()),
+                               (3 if act[0] > 1.5 else 2) if (mode == MODE_SILU and act[0] > 0.5) else int(xielu),
+                               c_float(act[1] if (mode == MODE_SILU and act[0] > 1.5) else act[0]), c_float(act[1]), _stream()),
            "gemm_tc")
     return Partial(ws) if sk > 1 else out
 
@@ -1232,7 +1238,9 @@ def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, 
     largest s + correction among the ``keep`` best of ``groups`` groups of neighbours (group score: its two
     largest s + correction) -> ``idx`` int32 [T, top]; ``wt`` float32 [T, top] = their s over the sum, times
     ``scale`` (``renorm`` False: the chosen s themselves, times ``scale``; ``correction`` None: the choice goes by s);
-    ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given. Two kernels: the
+    ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given. Without a correction and with one
+    group the choice goes by the sums w_router x themselves (the same order as their sigmoids, also where two float32
+    sigmoids have both reached 1), and ``scores`` then holds those sums. Two kernels: the
     scores (``scores`` float32 [T, E], scratch), then the choice."""
     _need(x, "x", None, 2), _need(w_router, "w_router", torch.float32, 2), _need(correction, "correction", torch.float32, 1)
     _need(w_shared_gate, "w_shared_gate", torch.float32, 1), _need(idx, "idx", torch.int32, 2), _need(wt, "wt", torch.float32, 2)

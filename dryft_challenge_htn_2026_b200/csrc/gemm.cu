@@ -3,7 +3,8 @@
 //
 //  * sgemm: true float32 on CUDA cores (FMA, no tensor-core mode), any M, N, K. Each output is
 //    one sequential sum over K, so a row's result does not depend on the other rows of the batch.
-//    Epilogues: 0/1 store, 2 W = [gate; up]: store silu(gate)*up (with act_pos = 1: the tanh form of GELU instead of SiLU).
+//    Epilogues: 0/1 store, 2 W = [gate; up]: store silu(gate)*up (with act_pos = 1: the tanh form of GELU instead of SiLU;
+//    act_pos = 2: g' = min(gate, L), u' = clamp(up, -L, L), store g' sigmoid(1.702 g') (u' + 1) with L = act_neg).
 //  * sum_partials: adds up the float32 partial sums of a split-K bfloat16 product for a consumer
 //    that cannot do it while it reads.
 #include "common.cuh"
@@ -66,7 +67,14 @@ sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int
             const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
             if (m < M && n < N) {
                 float v = acc[i][j];
-                if (SILU) v = v / (1.f + expf(-gate_arg(v, act_pos > 0.5f))) * acu[i][j];   // act_pos 1: GELU gate
+                if (SILU) {
+                    if (act_pos > 1.5f) {     // act_pos 2: the clamped gate with the limit act_neg
+                        const float g = fminf(v, act_neg), u = fminf(fmaxf(acu[i][j], -act_neg), act_neg);
+                        v = g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+                    } else {
+                        v = v / (1.f + expf(-gate_arg(v, act_pos > 0.5f))) * acu[i][j];   // act_pos 1: GELU gate
+                    }
+                }
                 if (XIELU) v = xielu_f(v, act_pos, act_neg);
                 out[(size_t)m * N + n] = v;
             }
@@ -77,7 +85,7 @@ sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int
 DK_EXPORT int dk_sgemm(const float* x, const float* W, float* out, int M, int N, int K, int mode, float act_pos, float act_neg,
                        cudaStream_t st) {
     dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
-    if (mode == 2) return dk_launch(sgemm_kernel<true, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, act_pos, 0.f);
+    if (mode == 2) return dk_launch(sgemm_kernel<true, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, act_pos, act_neg);
     if (mode == 3) return dk_launch(sgemm_kernel<false, true>, grid, dim3(256), 0, st, x, W, out, M, N, K, act_pos, act_neg);
     return dk_launch(sgemm_kernel<false, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, 0.f, 0.f);
 }

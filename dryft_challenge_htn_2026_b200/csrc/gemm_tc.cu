@@ -142,6 +142,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // The gate of a gated product: v * sigmoid(a) with a = v for SiLU, and a = 2 sqrt(2/pi) (v + 0.044715 v^3) for the tanh
 // form of GELU (0.5 v (1 + tanh(u)) = v sigmoid(2u)).
 __device__ __forceinline__ float gate_arg(float v, bool gelu) { return gelu ? 1.5957691216057308f * v * fmaf(0.044715f * v, v, 1.f) : v; }
+// act 3 (mode 2): the clamped gate, g' = min(g, L), u' = clamp(u, -L, L): g' sigmoid(1.702 g') (u' + 1); else SiLU or GELU times up
+__device__ __forceinline__ float gated(float g, float u, int act, float limit) {
+    if (act == 3) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+    }
+    return __fdividef(g, 1.f + __expf(-gate_arg(g, act == 2))) * u;     // 2 ulp: far below the bf16 rounding that follows
+}
 struct QkvEpilogue {
     bf16 *q_out, *k_store, *v_store;
     const float *qn, *kn, *cos_t, *sin_t;
@@ -149,7 +158,7 @@ struct QkvEpilogue {
     int pt_stride, nh, nkv, hd, write_kv;
     float eps;
     // an activation on the finished sums before they are stored (never on partial sums): mode 0: 1 = xIELU;
-    // mode 2: 2 = the gate through the tanh form of GELU instead of SiLU
+    // mode 2: 2 = the gate through the tanh form of GELU instead of SiLU, 3 = the clamped gate with the limit act_pos
     int act;
     float act_pos, act_neg;
 };
@@ -498,11 +507,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         float4 f = *reinterpret_cast<const float4*>(stg + r * LD + c);
                         if (MODE == 2) {
                             const float4 up = *reinterpret_cast<const float4*>(stg + r * LD + OUT_COLS + c);
-                            const bool gelu = qe.act == 2;
-                            f.x = __fdividef(f.x, 1.f + __expf(-gate_arg(f.x, gelu))) * up.x;   // 2 ulp: far below the bf16 rounding that follows
-                            f.y = __fdividef(f.y, 1.f + __expf(-gate_arg(f.y, gelu))) * up.y;
-                            f.z = __fdividef(f.z, 1.f + __expf(-gate_arg(f.z, gelu))) * up.z;
-                            f.w = __fdividef(f.w, 1.f + __expf(-gate_arg(f.w, gelu))) * up.w;
+                            f.x = gated(f.x, up.x, qe.act, qe.act_pos);
+                            f.y = gated(f.y, up.y, qe.act, qe.act_pos);
+                            f.z = gated(f.z, up.z, qe.act, qe.act_pos);
+                            f.w = gated(f.w, up.w, qe.act, qe.act_pos);
                         }
                         if (MODE == 0 && qe.act == 1 && ws == nullptr) {
                             f.x = xielu_f(f.x, qe.act_pos, qe.act_neg), f.y = xielu_f(f.y, qe.act_pos, qe.act_neg);
@@ -551,7 +559,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     // step made this epilogue 10 us longer
                     if (row < M) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) f[i] = __fdividef(f[i], 1.f + __expf(-gate_arg(f[i], qe.act == 2))) * __uint_as_float(u[i]);   // 2 ulp: far below the bf16 rounding that follows
+                        for (int i = 0; i < 32; i++) f[i] = gated(f[i], __uint_as_float(u[i]), qe.act, qe.act_pos);
                     }
                 }
                 if (MODE == 0 && qe.act == 1 && ws == nullptr && row < M) {
@@ -677,10 +685,10 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
 // float32). bn: weight rows a tile, a multiple of 16 from 128 to 256 (mode 2: half of them gate
 // rows, half up rows): the planner picks the height whose tiles and slices load the SMs most evenly.
 // act = 1 (mode 0, SK = 1, bfloat16 out): xIELU with the two constants on the sums before they are stored.
-// act = 2 (mode 2): the gate goes through the tanh form of GELU instead of SiLU.
+// act = 2 (mode 2): the gate goes through the tanh form of GELU instead of SiLU; act = 3 (mode 2): the clamped gate with limit act_pos.
 DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, int SK, float* ws,
                          int bn, int act, float act_pos, float act_neg, cudaStream_t st) {
-    if (act != 0 && !(act == 1 && mode == 0 && SK == 1 && ws == nullptr) && !(act == 2 && mode == 2)) return (int)cudaErrorInvalidValue;
+    if (act != 0 && !(act == 1 && mode == 0 && SK == 1 && ws == nullptr) && !((act == 2 || act == 3) && mode == 2)) return (int)cudaErrorInvalidValue;
     QkvEpilogue qe{};
     qe.act = act, qe.act_pos = act_pos, qe.act_neg = act_neg;
     if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr || SK < 1) return (int)cudaErrorInvalidValue;

@@ -189,7 +189,12 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
                         float up = 0.f;
 #pragma unroll
                         for (int w = 0; w < WARPS; w++) up += sums[w * (WR * MR) + (8 + i) * MR + j];
-                        v = v / (1.f + expf(-gate_arg(v, act_pos > 0.5f))) * up;   // act_pos 1: GELU gate
+                        if (act_pos > 1.5f) {     // act_pos 2: the clamped gate with the limit act_neg
+                            const float g = fminf(v, act_neg), u = fminf(fmaxf(up, -act_neg), act_neg);
+                            v = g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+                        } else {
+                            v = v / (1.f + expf(-gate_arg(v, act_pos > 0.5f))) * up;   // act_pos 1: GELU gate
+                        }
                     }
                     if (MODE == 3) v = xielu_f(v, act_pos, act_neg);
                     if (SK > 1) ws[((size_t)slice * M + j) * N + n] = v;
@@ -284,7 +289,8 @@ DK_EXPORT long long dk_gemv_stream_smem(int rows, int K, int SK, int warps) {
 // multiple of SK; `warps` streaming warps a block, 4 or 8. Refused (cudaErrorInvalidValue) when the
 // rows of a slice do not fit the shared memory of a block of that shape.
 // Mode 3: as mode 0 with xIELU (constants act_pos, act_neg) on the sums before they are stored; SK = 1.
-// Mode 2 with act_pos = 1: the gate goes through the tanh form of GELU instead of SiLU.
+// Mode 2 with act_pos = 1: the gate goes through the tanh form of GELU instead of SiLU; with act_pos = 2: the clamped gate
+// g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1) with L = act_neg.
 DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws, int M, int N, int K, int mode, int SK,
                              int blocks, int warps, float act_pos, float act_neg, cudaStream_t st) {
     if (M < 1 || M > 16 || K % 16 != 0 || SK < 1 || blocks < SK || (warps != 4 && warps != 8)) return (int)cudaErrorInvalidValue;
@@ -296,7 +302,7 @@ DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws,
     if (mode == 0) return launch<MR, 0, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);        \
     if (mode == 1) return launch<MR, 1, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);        \
     if (mode == 3) return launch<MR, 3, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st, act_pos, act_neg); \
-    return launch<MR, 2, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st, act_pos, 0.f);
+    return launch<MR, 2, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st, act_pos, act_neg);
 #define GS_CASE(MR)                   \
     if (warps == 4) { GS_MODE(MR, 4) } \
     GS_MODE(MR, 8)

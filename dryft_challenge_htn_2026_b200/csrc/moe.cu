@@ -33,7 +33,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_scores_kernel(const T* x, int W, const float* __restrict__ wr, const float* __restrict__ wsg, int E, float* scores,
-                  float* sgate, int n_tok) {
+                  float* sgate, int n_tok, int by_logit) {
     extern __shared__ __align__(16) unsigned char route_smem[];
     T* xs = reinterpret_cast<T*>(route_smem);          // [ROUTE_TOKENS][W]
     pdl_wait();
@@ -88,7 +88,7 @@ moe_scores_kernel(const T* x, int W, const float* __restrict__ wr, const float* 
         const float z = warp_sum(acc[tt]);
         if (lane == 0) {
             const float sg = 1.f / (1.f + expf(-z));
-            if (e < E) scores[(size_t)(t0 + tt) * E + e] = sg;
+            if (e < E) scores[(size_t)(t0 + tt) * E + e] = by_logit ? z : sg;     // the sum itself where the choice goes by it
             else sgate[t0 + tt] = sg;
         }
     }
@@ -97,7 +97,7 @@ moe_scores_kernel(const T* x, int W, const float* __restrict__ wr, const float* 
 // Choice: a warp a token, from the token's scores.
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_choose_kernel(const float* scores, const float* __restrict__ corr, int E, int top, int groups, int keep, float scale,
-                  int* idx, float* wt, int n_tok, int renorm) {
+                  int* idx, float* wt, int n_tok, int renorm, int by_logit) {
     extern __shared__ __align__(16) unsigned char route_smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -108,8 +108,15 @@ moe_choose_kernel(const float* scores, const float* __restrict__ corr, int E, in
     float* c = s + E;
     float* gs = c + E;
     for (int e = lane; e < E; e += 32) {
-        s[e] = scores[(size_t)t * E + e];
-        c[e] = s[e] + (corr ? corr[e] : 0.f);
+        const float v = scores[(size_t)t * E + e];
+        if (by_logit) {      // no correction, one group: the largest scores are the largest sums, and two float32 scores that
+                             // have both reached 1 still differ in their sums
+            s[e] = 1.f / (1.f + expf(-v));
+            c[e] = v;
+        } else {
+            s[e] = v;
+            c[e] = v + (corr ? corr[e] : 0.f);
+        }
     }
     __syncwarp();
     if (groups > 1 && keep < groups) {
@@ -288,13 +295,13 @@ moe_down_rows_kernel(const T* mid, const T* __restrict__ wd, const int* idx, con
 
 template <typename T>
 static int launch_scores(const void* x, int W, const float* wr, const float* wsg, int E, float* scores, float* sgate, int n_tok,
-                         cudaStream_t st) {
+                         int by_logit, cudaStream_t st) {
     const size_t smem = sizeof(T) * (size_t)ROUTE_TOKENS * W;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int rows = E + (wsg != nullptr ? 1 : 0);
     return dk_launch(moe_scores_kernel<T>, dim3((n_tok + ROUTE_TOKENS - 1) / ROUTE_TOKENS, (rows + ROUTE_WARPS - 1) / ROUTE_WARPS),
-                     dim3(32 * ROUTE_WARPS), smem, st, (const T*)x, W, wr, wsg, E, scores, sgate, n_tok);
+                     dim3(32 * ROUTE_WARPS), smem, st, (const T*)x, W, wr, wsg, E, scores, sgate, n_tok, by_logit);
 }
 
 // scores: float32 scratch [n_tok, E]
@@ -304,12 +311,13 @@ DK_EXPORT int dk_moe_route(int dtype, const void* x, int W, const float* wr, con
     if (E < 1 || E > MOE_MAX_EXPERTS || top < 1 || top > 32 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups ||
         scores == nullptr || (sizeof(float) * ROUTE_TOKENS * W > 200 * 1024))
         return (int)cudaErrorInvalidValue;
-    int e = dtype == 0 ? launch_scores<float>(x, W, wr, wsg, E, scores, sgate, n_tok, st)
-                       : launch_scores<bf16>(x, W, wr, wsg, E, scores, sgate, n_tok, st);
+    const int by_logit = corr == nullptr && groups == 1;
+    int e = dtype == 0 ? launch_scores<float>(x, W, wr, wsg, E, scores, sgate, n_tok, by_logit, st)
+                       : launch_scores<bf16>(x, W, wr, wsg, E, scores, sgate, n_tok, by_logit, st);
     if (e) return e;
     const size_t smem = sizeof(float) * 3 * (size_t)E * ROUTE_WARPS;
     return dk_launch(moe_choose_kernel, dim3((n_tok + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(32 * ROUTE_WARPS), smem, st, scores, corr,
-                     E, top, groups, keep, scale, idx, wt, n_tok, renorm);
+                     E, top, groups, keep, scale, idx, wt, n_tok, renorm, by_logit);
 }
 
 template <typename T, bool VEC>

@@ -16,7 +16,7 @@ STORE, STORE_F32, SILU, XIELU = api.MODE_STORE, api.MODE_STORE_F32, api.MODE_SIL
 def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
     """mode STORE: [M, N] in x's dtype; STORE_F32: float32 (logits); SILU: w = [gate; up] rows,
     returns silu(x.gate^T) * (x.up^T) of width N/2 (with ``act`` = ``api.GATE_GELU`` the gate goes through the tanh
-    form of GELU instead); XIELU: xielu(x.w^T) with the constants ``act`` =
+    form of GELU instead, with ``api.gate_clamped(limit)`` through the clamped gate); XIELU: xielu(x.w^T) with the constants ``act`` =
     (alpha_pos, alpha_neg), in the product's epilogue wherever the product is this library's (after
     the library's product a row kernel applies it). ``allow_partial``: the caller can take
     ``csrc.api.Partial`` (split-K partial sums, added up by the kernel that consumes them) instead
@@ -35,7 +35,10 @@ def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
         out = torch.mm(x, w.t())
         if mode == SILU:
             half = torch.empty((M, N), dtype=x.dtype, device=x.device)
-            api.act_mul(out, half, api.ACT_GELU_TANH if act[0] > 0.5 else api.ACT_SILU)
+            if act[0] > 1.5:
+                api.act_mul(out, half, api.ACT_CLAMPED, act[1])
+            else:
+                api.act_mul(out, half, api.ACT_GELU_TANH if act[0] > 0.5 else api.ACT_SILU)
             return half
         if mode == XIELU:
             api.xielu(out, out, act[0], act[1])

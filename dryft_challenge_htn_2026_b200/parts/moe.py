@@ -81,11 +81,8 @@ class RoutedMLP(Part):
         api.moe_route(a, self.w_router, self.correction, self.w_shared_gate, s.top, s.groups, s.keep_groups, s.route_scale,
                       idx, wt, sgate, renorm=s.renorm)
         shared = None
-        if s.shared_ff is not None and s.activation == "clamped":
-            gu = linear(a, self.w_shared_gu)
-            half = torch.empty((T, s.shared_ff), dtype=self.rt.dtype, device=dev)
-            api.act_mul(gu, half, api.ACT_CLAMPED, s.shared_limit)
-            shared = linear(half, self.w_shared_down)
+        if s.shared_ff is not None and s.activation == "clamped":      # the clamped gate in the product's epilogue
+            shared = linear(linear(a, self.w_shared_gu, SILU, act=api.gate_clamped(s.shared_limit)), self.w_shared_down)
         elif s.shared_ff is not None:
             shared = linear(linear(a, self.w_shared_gu, SILU), self.w_shared_down)
         out = torch.empty((T, s.hidden_size), dtype=self.rt.dtype, device=dev)
