@@ -285,15 +285,27 @@ __global__ void attn_talk_merge_kernel(const float* ws_acc, const float* ws_ml, 
     }
     const float* ml = ws_ml + ((size_t)b * nh + h) * nsplit * 2;
     const float* acc = ws_acc + ((size_t)b * nh + h) * nsplit * HDV;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; s++) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    for (int s = 0; s < nsplit; s++) L += ml[2 * s + 1] * exp2f(ml[2 * s] - M);
-    for (int d = lane; d < HDV; d += 32) {
-        float v = 0.f;
-        for (int s = 0; s < nsplit; s++)
-            if (ml[2 * s + 1] > 0.f) v += acc[(size_t)s * HDV + d] * exp2f(ml[2 * s] - M);
-        o[d] = __float2bfloat16_rn(v / L * out_scale);
+    // lane s holds part s (nsplit <= 32): its maximum and sum in one trip, its weight 2^(m_s - M) handed round by shuffles
+    const float m_s = lane < nsplit ? ml[2 * lane] : -INFINITY;
+    const float l_s = lane < nsplit ? ml[2 * lane + 1] : 0.f;
+    const float M = warp_max(m_s);
+    const float w = l_s > 0.f ? exp2f(m_s - M) : 0.f;
+    const float inv = out_scale / warp_sum(l_s * w);
+    float v[HDV / 32 + 1];
+#pragma unroll
+    for (int i = 0; i < HDV / 32 + 1; i++) v[i] = 0.f;
+    for (int s = 0; s < nsplit; s++) {
+        const float ws = __shfl_sync(0xffffffffu, w, s);
+#pragma unroll
+        for (int i = 0; i < HDV / 32 + 1; i++) {
+            const int d = lane + 32 * i;
+            if (d < HDV) v[i] = fmaf(acc[(size_t)s * HDV + d], ws, v[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < HDV / 32 + 1; i++) {
+        const int d = lane + 32 * i;
+        if (d < HDV) o[d] = __float2bfloat16_rn(v[i] * inv);
     }
 }
 
@@ -307,7 +319,7 @@ DK_EXPORT int dk_attention_talk_bf16(const void* q, long long ldq, void* out, lo
                                      const void* v_store, const int* tiles, int n_tiles, const int* cu_q, const int* seq_pos0,
                                      const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window,
                                      float scale, const float* talk, int nsplit, float* ws_acc, float* ws_ml, cudaStream_t st) {
-    if (nh < 1 || nh > 64 || nkv < 1 || nh % nkv || nsplit < 1 || (nsplit > 1 && (tiles != nullptr || ws_acc == nullptr || ws_ml == nullptr)))
+    if (nh < 1 || nh > 64 || nkv < 1 || nh % nkv || nsplit < 1 || nsplit > 32 || (nsplit > 1 && (tiles != nullptr || ws_acc == nullptr || ws_ml == nullptr)))
         return (int)cudaErrorInvalidValue;
     // the query rows stay in shared memory where there is room (16-byte rows), else every run reads them from memory again
     // (a single token has one row: it is read from memory, and two blocks may share an SM)
